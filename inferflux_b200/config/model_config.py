@@ -488,3 +488,175 @@ class PemoraxConfig(ModelConfig):
             layers.append({"type": l.type, "mixer": {"left": strip(left), "right": strip(right)}, "mlp": mlp})
         return {"architecture": self.architecture, "width": self.width, "vocab": self.vocab,
                 "norm": {"eps": self.norm_eps}, "layers": layers}
+
+
+@dataclass(frozen=True)
+class TekosunLayer:
+    """One layer of a Tekosun model as config.json gives it: ``type`` (which mixer), the mixer's sizes and
+    constants (checked, defaults filled in) and its feed-forward (``None`` = none; else the experts' and the
+    shared expert's sizes and the router's constants)."""
+
+    type: str = ""
+    mixer: Dict[str, Any] = field(default_factory=dict)
+    mlp: Optional[Dict[str, Any]] = None
+
+
+@dataclass(frozen=True)
+class TekosunConfig(ModelConfig):
+    """``Tekosun``: a decoder whose layers are listed one by one in config.json (``layers``: ``type``, the mixer's
+    sizes under ``mixer``, the feed-forward under ``mlp`` or null).  The embedding is multiplied by
+    ``embedding.scale``.  A sublayer reads the stream itself; an RMS norm sits behind it.  Mixers: ``mamba2`` (a
+    selective state-space layer), ``general_delta`` (linear attention by the generalized delta rule) and
+    ``attention`` (grouped-query attention with a norm over the whole query and key projections, rotary positions
+    with an optional frequency scaling, a unit norm on every value head, an optional sliding window and an optional
+    blend of the values with those of the first such layer).  The feed-forward is a mixture of squared-relu
+    experts with a softmax router over all experts and a shared expert."""
+
+    width: int = 0
+    vocab: int = 0
+    norm_eps: float = 1e-6
+    embedding_scale: float = 1.0
+    layers: List[TekosunLayer] = field(default_factory=list)
+
+    ARCHITECTURE = "Tekosun"
+    MODEL_TYPE = "tekosun"
+    MIXERS = ("mamba2", "general_delta", "attention")
+
+    @staticmethod
+    def _opt_int(m: Dict[str, Any], key: str, default: int, minimum: int = 1) -> int:
+        return _require_int(m, key, minimum) if m.get(key) is not None else default
+
+    @classmethod
+    def _mamba2(cls, m: Dict[str, Any], where: str) -> Dict[str, Any]:
+        out = {"heads": _require_int(m, "heads"), "vdim": _require_int(m, "vdim"), "state": _require_int(m, "state"),
+               "groups": cls._opt_int(m, "groups", 1), "conv": _require_int(m, "conv"),
+               "norm_groups": cls._opt_int(m, "norm_groups", 1)}
+        if out["heads"] % out["groups"]:
+            raise ConfigError(f"{where}: heads {out['heads']} is not a multiple of groups {out['groups']}")
+        if (out["heads"] * out["vdim"]) % out["norm_groups"]:
+            raise ConfigError(f"{where}: heads * vdim is not a multiple of norm_groups {out['norm_groups']}")
+        if out["conv"] > 16:
+            raise ConfigError(f"{where}: a convolution of {out['conv']} taps is not supported (at most 16)")
+        if out["state"] > 512:
+            raise ConfigError(f"{where}: a state of {out['state']} rows is not supported (at most 512)")
+        return out
+
+    @classmethod
+    def _general_delta(cls, m: Dict[str, Any], where: str) -> Dict[str, Any]:
+        out = {"heads": _require_int(m, "heads"), "dim": _require_int(m, "dim"),
+               "decay_rank": cls._opt_int(m, "decay_rank", 0)}      # 0: the stored tensor's shape gives it
+        if out["dim"] > 512:
+            raise ConfigError(f"{where}: dim {out['dim']} is not supported (at most 512)")
+        return out
+
+    @classmethod
+    def _attention(cls, m: Dict[str, Any], where: str) -> Dict[str, Any]:
+        heads, dim = _require_int(m, "heads"), _require_int(m, "dim")
+        out = {"heads": heads, "kv_heads": cls._opt_int(m, "kv_heads", heads), "dim": dim, "vdim": cls._opt_int(m, "vdim", dim),
+               "scale": _require_number(m, "scale", where) if m.get("scale") is not None else float(dim) ** -0.5,
+               "v_mix": bool(m.get("v_mix") or False), "window": None, "rot": {"dims": 0, "base": 10000.0, "scaling": None}}
+        if heads % out["kv_heads"]:
+            raise ConfigError(f"{where}: heads {heads} is not a multiple of kv_heads {out['kv_heads']}")
+        if dim > 256 or out["vdim"] > 256:
+            raise ConfigError(f"{where}: dim and vdim must be at most 256")
+        mask = _sub(m, "mask", where, optional=True)
+        if mask is not None and mask.get("size") is not None:
+            out["window"] = _require_int(mask, "size")
+        rot = _sub(m, "rot", where, optional=True)
+        if rot is not None and rot.get("dims"):
+            dims = _require_int(rot, "dims")
+            if dims % 2 or dims > dim:
+                raise ConfigError(f"{where}: rot.dims {dims} must be even and at most dim {dim}")
+            base = _require_number(rot, "base", where + " rot")
+            if base <= 1.0:
+                raise ConfigError(f"{where}: rot.base must be above 1")
+            out["rot"] = {"dims": dims, "base": base, "scaling": None}
+            sc = _sub(rot, "scaling", where + " rot", optional=True)
+            if sc is not None:
+                out["rot"]["scaling"] = {k: _require_number(sc, k, where + " rot.scaling") for k in ("factor", "low", "high", "original")}
+                s = out["rot"]["scaling"]
+                if min(s.values()) <= 0 or s["high"] == s["low"]:
+                    raise ConfigError(f"{where}: the numbers of rot.scaling must be positive, high and low different")
+        return out
+
+    @classmethod
+    def _mlp(cls, mlp: Dict[str, Any], where: str) -> Dict[str, Any]:
+        kind = mlp.get("kind", "moe")
+        if kind != "moe":
+            raise ConfigError(f"{where}: mlp kind {kind!r} is not one of ['moe']")
+        router = _sub(mlp, "router", where)
+        out = {"kind": "moe", "ff": _require_int(_sub(mlp, "expert", where), "ff"), "experts": _require_int(router, "experts"),
+               "top": _require_int(router, "top"),
+               "scale": _require_number(router, "scale", where + " router") if router.get("scale") is not None else 1.0,
+               "shared_ff": None}
+        if out["top"] > out["experts"]:
+            raise ConfigError(f"{where}: router.top {out['top']} exceeds router.experts {out['experts']}")
+        if out["top"] > 64:
+            raise ConfigError(f"{where}: router.top {out['top']} is not supported (at most 64)")
+        shared = _sub(mlp, "shared", where, optional=True)
+        if shared is not None:
+            out["shared_ff"] = _require_int(shared, "ff")
+        return out
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "TekosunConfig":
+        width, vocab = _require_int(d, "width"), _require_int(d, "vocab")
+        eps = _require_number(_sub(d, "norm", "config.json"), "eps", "config.json norm")
+        if eps <= 0:
+            raise ConfigError(f"norm eps must be positive, got {eps}")
+        emb = _sub(d, "embedding", "config.json", optional=True) or {}
+        scale = _require_number(emb, "scale", "config.json embedding") if emb.get("scale") is not None else 1.0
+        raw = d.get("layers")
+        if not isinstance(raw, list) or not raw:
+            raise ConfigError("config.json: 'layers' must be a non-empty list")
+        layers, first_mix = [], None
+        for i, entry in enumerate(raw):
+            where = f"config.json layers[{i}]"
+            if not isinstance(entry, dict):
+                raise ConfigError(f"{where}: must be an object")
+            kind = entry.get("type")
+            if kind not in cls.MIXERS:
+                raise ConfigError(f"{where}: type {kind!r} is not one of {list(cls.MIXERS)}")
+            mixer = getattr(cls, "_" + kind)(_sub(entry, "mixer", where), where + " mixer")
+            if kind == "attention" and mixer["v_mix"]:
+                sizes = (mixer["kv_heads"], mixer["vdim"])
+                if first_mix is None:
+                    first_mix = sizes
+                elif sizes != first_mix:
+                    raise ConfigError(f"{where}: a layer with v_mix has kv_heads, vdim {sizes}, the first such layer {first_mix}")
+            mlp = _sub(entry, "mlp", where, optional=True)
+            layers.append(TekosunLayer(type=kind, mixer=mixer, mlp=cls._mlp(mlp, where + " mlp") if mlp is not None else None))
+        arch = d.get("architecture") or (d.get("architectures") or [cls.ARCHITECTURE])[0]
+        return cls(architectures=[str(arch)], model_type=str(d.get("model_type", "") or cls.MODEL_TYPE), width=width,
+                   vocab=vocab, norm_eps=eps, embedding_scale=scale, layers=layers)
+
+    @property
+    def vocab_size(self) -> int:
+        return self.vocab
+
+    @property
+    def eos_token_id(self) -> Optional[int]:
+        return None
+
+    def to_dict(self) -> Dict[str, Any]:
+        """The config.json this configuration was read from (its own keys)."""
+        layers = []
+        for l in self.layers:
+            m = dict(l.mixer)
+            if l.type == "attention":
+                rot, window = m.pop("rot"), m.pop("window")
+                if rot["dims"]:
+                    m["rot"] = {k: v for k, v in rot.items() if v is not None}
+                if window:
+                    m["mask"] = {"size": window}
+            elif l.type == "general_delta" and not m["decay_rank"]:
+                m.pop("decay_rank")
+            mlp = None
+            if l.mlp:
+                mlp = {"kind": "moe", "expert": {"ff": l.mlp["ff"]},
+                       "router": {"experts": l.mlp["experts"], "top": l.mlp["top"], "scale": l.mlp["scale"]}}
+                if l.mlp["shared_ff"]:
+                    mlp["shared"] = {"ff": l.mlp["shared_ff"]}
+            layers.append({"type": l.type, "mixer": m, "mlp": mlp})
+        return {"architecture": self.architecture, "width": self.width, "vocab": self.vocab, "norm": {"eps": self.norm_eps},
+                "embedding": {"scale": self.embedding_scale}, "layers": layers}

@@ -14,7 +14,7 @@
 // ---------------------------------------------------------------- embedding
 template <typename T>
 __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                                    float* __restrict__ out, int hidden, int vocab) {
+                                    float* __restrict__ out, int hidden, int vocab, float scale) {
   pdl_enter();
   const int t = blockIdx.x;
   const int id = ids[t];
@@ -24,12 +24,12 @@ __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __re
     return;
   }
   const T* row = table + (size_t)id * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = Num<T>::to_f(row[i]);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = Num<T>::to_f(row[i]) * scale;
 }
 
 // 8 bfloat16 (16 bytes) per thread per step; hidden a multiple of 8
 __global__ void embed_gather_bf16x8_kernel(const bf16* __restrict__ table, const int* __restrict__ ids,
-                                           float* __restrict__ out, int hidden, int vocab) {
+                                           float* __restrict__ out, int hidden, int vocab, float scale) {
   pdl_enter();
   const int t = blockIdx.x;
   const int id = ids[t];
@@ -41,22 +41,23 @@ __global__ void embed_gather_bf16x8_kernel(const bf16* __restrict__ table, const
     const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
     const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
     const float2 c = __bfloat1622float2(h[2]), d = __bfloat1622float2(h[3]);
-    o[2 * i] = make_float4(a.x, a.y, b.x, b.y);
-    o[2 * i + 1] = make_float4(c.x, c.y, d.x, d.y);
+    o[2 * i] = make_float4(a.x * scale, a.y * scale, b.x * scale, b.y * scale);
+    o[2 * i + 1] = make_float4(c.x * scale, c.y * scale, d.x * scale, d.y * scale);
   }
 }
 
+// out[t] = float32(table[ids[t]]) * scale (the product in float32; scale 1 leaves the row as it is)
 IFX_API int ifx_embed_gather(const void* table, int table_dtype, const int* ids, float* out,
-                             int n_tokens, int hidden, int vocab, cudaStream_t stream) {
+                             int n_tokens, int hidden, int vocab, float scale, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   int ifx_rc = 0;
   const int threads = hidden >= 1024 ? 256 : (hidden >= 256 ? 128 : 64);
   if (table_dtype == IFX_F32)
-    ifx_rc = launch_pdl(embed_gather_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, (const float*)table, ids, out, hidden, vocab);
+    ifx_rc = launch_pdl(embed_gather_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, (const float*)table, ids, out, hidden, vocab, scale);
   else if (table_dtype == IFX_BF16 && hidden % 8 == 0 && ((uintptr_t)table & 15) == 0 && ((uintptr_t)out & 15) == 0)
-    ifx_rc = launch_pdl(embed_gather_bf16x8_kernel, dim3(n_tokens), dim3(threads), 0, stream, (const bf16*)table, ids, out, hidden, vocab);
+    ifx_rc = launch_pdl(embed_gather_bf16x8_kernel, dim3(n_tokens), dim3(threads), 0, stream, (const bf16*)table, ids, out, hidden, vocab, scale);
   else if (table_dtype == IFX_BF16)
-    ifx_rc = launch_pdl(embed_gather_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, stream, (const bf16*)table, ids, out, hidden, vocab);
+    ifx_rc = launch_pdl(embed_gather_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, stream, (const bf16*)table, ids, out, hidden, vocab, scale);
   else
     return IFX_ERR_UNSUPPORTED;
   return ifx_rc ? ifx_rc : IFX_LAUNCH_CHECK();
@@ -480,6 +481,51 @@ IFX_API int ifx_gelu_tanh(const float* z, int parts, long long part_stride, void
     rc = launch_pdl(gelu_tanh_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, z, parts, part_stride, (float*)out, out_stride, cols, total);
   else if (out_dtype == IFX_BF16)
     rc = launch_pdl(gelu_tanh_kernel<bf16>, dim3((int)blocks), dim3(256), 0, stream, z, parts, part_stride, (bf16*)out, out_stride, cols, total);
+  else
+    return IFX_ERR_UNSUPPORTED;
+  return rc ? rc : IFX_LAUNCH_CHECK();
+}
+
+// ---- one-argument activations over float32 sums, rounded once into the engine's type ----------------
+// out[m][c] = act(sum over slices of z[m][c]);  z rows z_stride elements apart (a block of columns of a wider
+// projection), slices part_stride apart.  act: 0 gelu (tanh form), 1 tanh, 2 relu(z)^2, 3 silu, 4 sigmoid.
+__device__ __forceinline__ float apply_activation(float v, int act) {
+  switch (act) {
+    case 0: return 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+    case 1: return tanhf(v);
+    case 2: { const float r = fmaxf(v, 0.0f); return r * r; }
+    case 3: return v / (1.0f + expf(-v));
+    default: return 1.0f / (1.0f + expf(-v));
+  }
+}
+
+template <typename T>
+__global__ void activation_kernel(const float* __restrict__ z, long long z_stride, int parts, long long part_stride,
+                                  T* __restrict__ out, long long out_stride, int cols, long long total, int act) {
+  pdl_enter();
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (; idx < total; idx += stride) {
+    const long long m = idx / cols;
+    const int c = (int)(idx - m * cols);
+    float v = 0.0f;
+    for (int s = 0; s < parts; ++s) v += z[(size_t)s * part_stride + m * z_stride + c];
+    out[m * out_stride + c] = Num<T>::from_f(apply_activation(v, act));
+  }
+}
+
+IFX_API int ifx_activation(const float* z, long long z_stride, int parts, long long part_stride, void* out, int out_dtype,
+                           long long out_stride, int m, int cols, int act, cudaStream_t stream) {
+  const long long total = (long long)m * cols;
+  if (total <= 0) return 0;
+  if (act < 0 || act > 4) return IFX_ERR_UNSUPPORTED;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  int rc;
+  if (out_dtype == IFX_F32)
+    rc = launch_pdl(activation_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, z, z_stride, parts, part_stride, (float*)out, out_stride, cols, total, act);
+  else if (out_dtype == IFX_BF16)
+    rc = launch_pdl(activation_kernel<bf16>, dim3((int)blocks), dim3(256), 0, stream, z, z_stride, parts, part_stride, (bf16*)out, out_stride, cols, total, act);
   else
     return IFX_ERR_UNSUPPORTED;
   return rc ? rc : IFX_LAUNCH_CHECK();

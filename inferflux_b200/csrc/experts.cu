@@ -15,9 +15,11 @@
 
 namespace {
 constexpr int MAX_TOP = 64;
+// what a tile product does with its sums: nothing; W_e = [gate rows; up rows] and out = silu(gate) * up; out = relu(sum)^2
+constexpr int MODE_PLAIN = 0, MODE_SWIGLU = 1, MODE_RELU2 = 2;
 
 __global__ void __launch_bounds__(256)
-moe_route_kernel(const float* __restrict__ logits, int n_tokens, int experts, int top,
+moe_route_kernel(const float* __restrict__ logits, int n_tokens, int experts, int top, int over_all, float scale,
                  int* __restrict__ chosen, float* __restrict__ weights) {
   pdl_enter();
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
@@ -39,11 +41,24 @@ moe_route_kernel(const float* __restrict__ logits, int n_tokens, int experts, in
     }
     ids[k] = arg; vals[k] = best;
   }
+  if (over_all) {
+    // scores are the softmax over every expert; a chosen one's weight is its score over the chosen scores' sum
+    float all = 0.0f;
+    for (int e = lane; e < experts; e += 32) all += expf(z[e] - vals[0]);
+    all = warp_sum(all);
+    float sum = 0.0f;
+    for (int k = 0; k < top; ++k) sum += expf(vals[k] - vals[0]) / all;
+    for (int k = lane; k < top; k += 32) {
+      chosen[(size_t)t * top + k] = ids[k];
+      weights[(size_t)t * top + k] = expf(vals[k] - vals[0]) / all / (sum + 1e-20f) * scale;
+    }
+    return;
+  }
   float sum = 0.0f;
   for (int k = 0; k < top; ++k) sum += expf(vals[k] - vals[0]);      // vals[0] is the largest
   for (int k = lane; k < top; k += 32) {
     chosen[(size_t)t * top + k] = ids[k];
-    weights[(size_t)t * top + k] = expf(vals[k] - vals[0]) / sum;
+    weights[(size_t)t * top + k] = expf(vals[k] - vals[0]) / sum * scale;
   }
 }
 
@@ -85,11 +100,12 @@ moe_group_kernel(const int* __restrict__ chosen, int pairs, int experts, int til
 // C tile = A rows (gathered) x W_e^T.  SWIGLU: W_e is [2 * n_out][K] (gate rows, then up rows) and the tile's
 // columns are n_out wide: out = silu(gate) * up in TO.  Otherwise W_e is [n_out][K] and out is float32.
 // BM = 16 * TM rows a tile.
-template <typename TA, typename TW, typename TO, int TM, bool SWIGLU>
+template <typename TA, typename TW, typename TO, int TM, int MODE>
 __global__ void __launch_bounds__(256)
 moe_product_kernel(const TA* __restrict__ A, long long lda, int gather_div /* 0: rows are sorted rows; else token = pair / gather_div */,
                    const TW* __restrict__ W, const int* __restrict__ tile_expert, const int* __restrict__ sorted_pair,
                    TO* __restrict__ C, long long ldc, int n_out, int K) {
+  constexpr bool SWIGLU = MODE == MODE_SWIGLU;
   constexpr int BM = 16 * TM, BN = 64, BK = 16;
   constexpr int TN = SWIGLU ? 2 : 4;                // per thread: TM x TN outputs (SWIGLU: of gate and of up each)
   pdl_enter();
@@ -158,6 +174,9 @@ moe_product_kernel(const TA* __restrict__ A, long long lda, int gather_div /* 0:
       if (SWIGLU) {
         const float g = acc[i][j], u = acc[i][2 + j];
         crow[n] = Num<TO>::from_f(g / (1.0f + expf(-g)) * u);
+      } else if (MODE == MODE_RELU2) {
+        const float r = fmaxf(acc[i][j], 0.0f);
+        crow[n] = Num<TO>::from_f(r * r);
       } else {
         crow[n] = Num<TO>::from_f(acc[i][j]);
       }
@@ -175,11 +194,12 @@ __device__ __forceinline__ void moe_mma_bf16(float (&d)[4], const unsigned (&a)[
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-template <typename TO, bool SWIGLU>
+template <typename TO, int MODE>
 __global__ void __launch_bounds__(128)
 moe_product_mma_kernel(const bf16* __restrict__ A, long long lda, int gather_div, const bf16* __restrict__ W,
                        const int* __restrict__ tile_expert, const int* __restrict__ sorted_pair, TO* __restrict__ C,
                        long long ldc, int n_out, int K) {
+  constexpr bool SWIGLU = MODE == MODE_SWIGLU;
   constexpr int BM = 16, BN = 64, BK = 64, LD = BK + 8;
   pdl_enter();
   __shared__ __align__(16) bf16 As[BM][LD];
@@ -246,8 +266,10 @@ moe_product_mma_kernel(const bf16* __restrict__ A, long long lda, int gather_div
         if (n < n_out) crow[n] = Num<TO>::from_f(gt / (1.0f + expf(-gt)) * up);
       } else {
         const int na = n0 + 16 * warp + 2 * t + j, nb = na + 8;
-        if (na < n_out) crow[na] = Num<TO>::from_f(acc0[2 * h + j]);
-        if (nb < n_out) crow[nb] = Num<TO>::from_f(acc1[2 * h + j]);
+        float va = acc0[2 * h + j], vb = acc1[2 * h + j];
+        if (MODE == MODE_RELU2) { va = fmaxf(va, 0.0f); va *= va; vb = fmaxf(vb, 0.0f); vb *= vb; }
+        if (na < n_out) crow[na] = Num<TO>::from_f(va);
+        if (nb < n_out) crow[nb] = Num<TO>::from_f(vb);
       }
     }
   }
@@ -266,26 +288,35 @@ moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pair_row
   }
 }
 
-int launch_products_mma(const void* x, const void* w_gate_up, const void* w_down, const int* tile_expert, const int* sorted_pair,
-                        void* act, float* y, int max_tiles, int hidden, int ff, int top, cudaStream_t stream) {
-  int rc = launch_pdl(moe_product_mma_kernel<bf16, true>, dim3((ff + 31) / 32, max_tiles), dim3(128), 0, stream,
-                      (const bf16*)x, (long long)hidden, top, (const bf16*)w_gate_up, tile_expert, sorted_pair, (bf16*)act,
-                      (long long)ff, ff, hidden);
+// act: MODE_SWIGLU (w_up = [gate rows; up rows] of every expert) or MODE_RELU2 (w_up = up rows alone)
+int launch_products_mma(const void* x, const void* w_up, const void* w_down, const int* tile_expert, const int* sorted_pair,
+                        void* act_out, float* y, int max_tiles, int hidden, int ff, int top, int act, cudaStream_t stream) {
+  int rc = act == MODE_SWIGLU
+      ? launch_pdl(moe_product_mma_kernel<bf16, MODE_SWIGLU>, dim3((ff + 31) / 32, max_tiles), dim3(128), 0, stream,
+                   (const bf16*)x, (long long)hidden, top, (const bf16*)w_up, tile_expert, sorted_pair, (bf16*)act_out,
+                   (long long)ff, ff, hidden)
+      : launch_pdl(moe_product_mma_kernel<bf16, MODE_RELU2>, dim3((ff + 63) / 64, max_tiles), dim3(128), 0, stream,
+                   (const bf16*)x, (long long)hidden, top, (const bf16*)w_up, tile_expert, sorted_pair, (bf16*)act_out,
+                   (long long)ff, ff, hidden);
   if (rc) return rc;
-  return launch_pdl(moe_product_mma_kernel<float, false>, dim3((hidden + 63) / 64, max_tiles), dim3(128), 0, stream,
-                    (const bf16*)act, (long long)ff, 0, (const bf16*)w_down, tile_expert, sorted_pair, y, (long long)hidden,
+  return launch_pdl(moe_product_mma_kernel<float, MODE_PLAIN>, dim3((hidden + 63) / 64, max_tiles), dim3(128), 0, stream,
+                    (const bf16*)act_out, (long long)ff, 0, (const bf16*)w_down, tile_expert, sorted_pair, y, (long long)hidden,
                     hidden, ff);
 }
 
 template <typename T, int TM>
-int launch_products(const void* x, const void* w_gate_up, const void* w_down, const int* tile_expert, const int* sorted_pair,
-                    void* act, float* y, int max_tiles, int hidden, int ff, int top, cudaStream_t stream) {
-  int rc = launch_pdl(moe_product_kernel<T, T, T, TM, true>, dim3((ff + 31) / 32, max_tiles), dim3(256), 0, stream,
-                      (const T*)x, (long long)hidden, top, (const T*)w_gate_up, tile_expert, sorted_pair, (T*)act,
-                      (long long)ff, ff, hidden);
+int launch_products(const void* x, const void* w_up, const void* w_down, const int* tile_expert, const int* sorted_pair,
+                    void* act_out, float* y, int max_tiles, int hidden, int ff, int top, int act, cudaStream_t stream) {
+  int rc = act == MODE_SWIGLU
+      ? launch_pdl(moe_product_kernel<T, T, T, TM, MODE_SWIGLU>, dim3((ff + 31) / 32, max_tiles), dim3(256), 0, stream,
+                   (const T*)x, (long long)hidden, top, (const T*)w_up, tile_expert, sorted_pair, (T*)act_out,
+                   (long long)ff, ff, hidden)
+      : launch_pdl(moe_product_kernel<T, T, T, TM, MODE_RELU2>, dim3((ff + 63) / 64, max_tiles), dim3(256), 0, stream,
+                   (const T*)x, (long long)hidden, top, (const T*)w_up, tile_expert, sorted_pair, (T*)act_out,
+                   (long long)ff, ff, hidden);
   if (rc) return rc;
-  return launch_pdl(moe_product_kernel<T, T, float, TM, false>, dim3((hidden + 63) / 64, max_tiles), dim3(256), 0, stream,
-                    (const T*)act, (long long)ff, 0, (const T*)w_down, tile_expert, sorted_pair, y, (long long)hidden,
+  return launch_pdl(moe_product_kernel<T, T, float, TM, MODE_PLAIN>, dim3((hidden + 63) / 64, max_tiles), dim3(256), 0, stream,
+                    (const T*)act_out, (long long)ff, 0, (const T*)w_down, tile_expert, sorted_pair, y, (long long)hidden,
                     hidden, ff);
 }
 }  // namespace
@@ -328,40 +359,45 @@ IFX_API int ifx_moe_combine(const float* y, const int* pair_row, const float* we
   return rc ? rc : IFX_LAUNCH_CHECK();
 }
 
-IFX_API int ifx_moe_route(const float* logits, int n_tokens, int experts, int top, int* chosen, float* weights,
-                          cudaStream_t stream) {
+// over_all 0: weights are the softmax over the chosen logits alone; 1: the softmax over every expert's logit, the
+// chosen ones' scores divided by their sum (+ 1e-20).  Either is multiplied by scale.
+IFX_API int ifx_moe_route(const float* logits, int n_tokens, int experts, int top, int over_all, float scale, int* chosen,
+                          float* weights, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (top < 1 || top > MAX_TOP || top > experts) return IFX_ERR_UNSUPPORTED;
   const int rc = launch_pdl(moe_route_kernel, dim3((n_tokens + 7) / 8), dim3(256), 0, stream, logits, n_tokens, experts, top,
-                            chosen, weights);
+                            over_all, scale, chosen, weights);
   return rc ? rc : IFX_LAUNCH_CHECK();
 }
 
 // Rows per tile for a step of n_tokens * top pairs: few pairs (single-token steps) take short tiles.
 IFX_API int ifx_moe_tile_rows(int pairs) { return pairs <= 256 ? 16 : 64; }
 
+// act 1: w_gate_up [experts][2 ff][hidden] and silu(gate) * up; act 2: w_gate_up [experts][ff][hidden] (up rows alone) and
+// relu(up)^2.
 // x [N][hidden], w_gate_up [experts][2 ff][hidden], w_down [experts][hidden][ff] of one element type `dtype`;
 // act [max_tiles * tile][ff] of that type, y [max_tiles * tile][hidden] float32, out [N][hidden] float32.
 // max_tiles >= pairs / tile + experts, tile = ifx_moe_tile_rows(pairs).
 IFX_API int ifx_moe_experts(const void* x, int dtype, const void* w_gate_up, const void* w_down, const int* chosen,
-                            const float* weights, int n_tokens, int hidden, int ff, int experts, int top, int tile,
+                            const float* weights, int n_tokens, int hidden, int ff, int experts, int top, int activation, int tile,
                             int max_tiles, int* tile_expert, int* sorted_pair, int* pair_row, void* act, float* y,
                             float* out, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   const int pairs = n_tokens * top;
   if ((tile != 16 && tile != 64) || max_tiles < pairs / tile + experts || experts > 4096) return IFX_ERR_UNSUPPORTED;
+  if (activation != MODE_SWIGLU && activation != MODE_RELU2) return IFX_ERR_UNSUPPORTED;
   int rc = launch_pdl(moe_group_kernel, dim3(1), dim3(1024), (size_t)3 * experts * sizeof(int), stream, chosen, pairs, experts,
                       tile, max_tiles, tile_expert, sorted_pair, pair_row);
   if (rc) return rc;
   if (dtype == IFX_F32)
-    rc = tile == 16 ? launch_products<float, 1>(x, w_gate_up, w_down, tile_expert, sorted_pair, act, y, max_tiles, hidden, ff, top, stream)
-                    : launch_products<float, 4>(x, w_gate_up, w_down, tile_expert, sorted_pair, act, y, max_tiles, hidden, ff, top, stream);
+    rc = tile == 16 ? launch_products<float, 1>(x, w_gate_up, w_down, tile_expert, sorted_pair, act, y, max_tiles, hidden, ff, top, activation, stream)
+                    : launch_products<float, 4>(x, w_gate_up, w_down, tile_expert, sorted_pair, act, y, max_tiles, hidden, ff, top, activation, stream);
   else if (dtype == IFX_BF16 && tile == 16 && hidden % 8 == 0 && ff % 8 == 0 &&
            (((uintptr_t)x | (uintptr_t)w_gate_up | (uintptr_t)w_down | (uintptr_t)act) & 15) == 0)
-    rc = launch_products_mma(x, w_gate_up, w_down, tile_expert, sorted_pair, act, y, max_tiles, hidden, ff, top, stream);
+    rc = launch_products_mma(x, w_gate_up, w_down, tile_expert, sorted_pair, act, y, max_tiles, hidden, ff, top, activation, stream);
   else if (dtype == IFX_BF16)
-    rc = tile == 16 ? launch_products<bf16, 1>(x, w_gate_up, w_down, tile_expert, sorted_pair, act, y, max_tiles, hidden, ff, top, stream)
-                    : launch_products<bf16, 4>(x, w_gate_up, w_down, tile_expert, sorted_pair, act, y, max_tiles, hidden, ff, top, stream);
+    rc = tile == 16 ? launch_products<bf16, 1>(x, w_gate_up, w_down, tile_expert, sorted_pair, act, y, max_tiles, hidden, ff, top, activation, stream)
+                    : launch_products<bf16, 4>(x, w_gate_up, w_down, tile_expert, sorted_pair, act, y, max_tiles, hidden, ff, top, activation, stream);
   else
     return IFX_ERR_UNSUPPORTED;
   if (rc) return rc;

@@ -164,7 +164,7 @@ struct QkvEpilogue {
   int page_size, page_shift, n_heads, n_kv;
 };
 
-// MODE 0: out = A W^T (+ bias); 1: SwiGLU of the two halves of W; 2: few rows of A; 3: q, k, v with bias,
+// MODE 0: out = A W^T (+ bias) (4: relu(.)^2 of it); 1: SwiGLU of the two halves of W; 2: few rows of A; 3: q, k, v with bias,
 // rotation and cache write (tiles of two heads of 128).  In mode 2 the operands
 // change places, so that the 256 rows of a tile are rows of the weights and its (few) columns the tokens: the
 // kernel is given the weights as map_a (M = their rows) and the activations as map_w (n_out = the tokens, all
@@ -179,7 +179,7 @@ gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   // tile_expert (modes 0 and 1, or null): the rows of A are sorted by expert into groups of 256, tile_expert[i]
   // names the expert whose weights row tile i multiplies (its rows of W start at expert * expert_rows) or is
   // negative for a row tile that is not in use, which every role of the kernel skips.
-  constexpr bool SWIGLU = MODE == 1, SKINNY = MODE == 2, QKV = MODE == 3;
+  constexpr bool SWIGLU = MODE == 1, SKINNY = MODE == 2, QKV = MODE == 3, RELU2 = MODE == 4;
   pdl_enter();
   extern __shared__ unsigned char g_smem_raw[];
   __shared__ __align__(8) unsigned long long bars[2 * P_STAGES + 4];    // full[s], empty[s], acc_full[2], acc_empty[2]
@@ -404,6 +404,10 @@ gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 #pragma unroll
               for (int i = 0; i < 32; ++i) v[i] += col + i < n_out ? bias[col + i] : 0.0f;
             }
+            if (RELU2) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) { const float r = fmaxf(v[i], 0.0f); v[i] = r * r; }
+            }
             store_row32<TOut>(orow + col, v, min(min(32, tile_n - c * 32), n_out - col), vec && (col % 8 == 0));
           }
         }
@@ -491,10 +495,11 @@ int launch_gemm_pair(const void* A, long long lda, const void* W, const float* b
 
 // The same product over rows sorted by expert into groups of 256: row tile i of A multiplies the weights of
 // expert tile_expert[i] (W is [experts][n_out or 2 n_out][K] as one matrix) or is skipped when that is negative.
-template <bool SWIGLU, typename TOut>
+template <int MODE, typename TOut>
 int launch_gemm_grouped(const void* A, long long lda, const void* W, void* out, long long ldo, int M, int n_out, int K,
                         int experts, const int* tile_expert, int* error_flag, cudaStream_t stream) {
-  auto kern = gemm_umma_pair_kernel<SWIGLU ? 1 : 0, TOut>;
+  constexpr bool SWIGLU = MODE == 1;
+  auto kern = gemm_umma_pair_kernel<MODE, TOut>;
   static int sms = 0;
   if (!sms) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM);
@@ -625,22 +630,23 @@ IFX_API int ifx_gemm_umma_skinny(const void* X, long long ldx, const void* W, fl
 }
 
 // Rows of A sorted by expert in groups of 256 (M a multiple of 256): out[row] = A[row] W_e^T with e =
-// tile_expert[row / 256], rows of unused groups (negative) untouched.  swiglu: W_e = [gate rows; up rows],
-// out = silu(gate) * up in bfloat16; otherwise out float32 or bfloat16 by out_dtype.
+// tile_expert[row / 256], rows of unused groups (negative) untouched.  act 1: W_e = [gate rows; up rows],
+// out = silu(gate) * up in bfloat16; act 2: out = relu(sum)^2 in bfloat16; act 0: the sums, float32 or bfloat16 by out_dtype.
 IFX_API int ifx_gemm_umma_grouped(const void* A, long long lda, const void* W, void* out, long long ldo, int out_dtype,
-                                  int M, int n_out, int K, int swiglu, int experts, const int* tile_expert,
+                                  int M, int n_out, int K, int act, int experts, const int* tile_expert,
                                   int* error_flag, cudaStream_t stream) {
   if (M <= 0 || n_out <= 0) return 0;
-  if (K <= 0 || (K % 8) || (lda % 8) || (M % 256) || experts < 1 || !tile_expert) return IFX_ERR_UNSUPPORTED;
+  if (K <= 0 || (K % 8) || (lda % 8) || (M % 256) || experts < 1 || !tile_expert || act < 0 || act > 2) return IFX_ERR_UNSUPPORTED;
   if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return IFX_ERR_ALIGNMENT;
-  if (swiglu) {
+  if (act) {
     if (out_dtype != IFX_BF16) return IFX_ERR_UNSUPPORTED;
-    return launch_gemm_grouped<true, bf16>(A, lda, W, out, ldo, M, n_out, K, experts, tile_expert, error_flag, stream);
+    return act == 1 ? launch_gemm_grouped<1, bf16>(A, lda, W, out, ldo, M, n_out, K, experts, tile_expert, error_flag, stream)
+                    : launch_gemm_grouped<4, bf16>(A, lda, W, out, ldo, M, n_out, K, experts, tile_expert, error_flag, stream);
   }
   if (out_dtype == IFX_BF16)
-    return launch_gemm_grouped<false, bf16>(A, lda, W, out, ldo, M, n_out, K, experts, tile_expert, error_flag, stream);
+    return launch_gemm_grouped<0, bf16>(A, lda, W, out, ldo, M, n_out, K, experts, tile_expert, error_flag, stream);
   if (out_dtype == IFX_F32)
-    return launch_gemm_grouped<false, float>(A, lda, W, out, ldo, M, n_out, K, experts, tile_expert, error_flag, stream);
+    return launch_gemm_grouped<0, float>(A, lda, W, out, ldo, M, n_out, K, experts, tile_expert, error_flag, stream);
   return IFX_ERR_UNSUPPORTED;
 }
 

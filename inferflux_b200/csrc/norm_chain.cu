@@ -6,6 +6,7 @@
 //   if w_post:  y = N(y) * w_post                (a norm behind the sublayer)
 //   r = residual + y;   residual = r             (unless `rows` picks rows: then the residual stays)
 //   if out:  out = N(r) * w_next                 (the norm ahead of the next sublayer, engine type)
+//            or, without w_next, out = r          (a sublayer that reads the stream itself: its rounding alone)
 //
 // Blocks that sandwich every sublayer between two norms, and mixers whose result is the mean of two normed
 // branches, run all of their row-wise arithmetic here in one pass over the row.  The number of threads
@@ -76,10 +77,13 @@ norm_chain_kernel(ChainArgs p) {
     row[i] = v;
     sr = fmaf(v, v, sr);
   }
-  if (p.out) {
+  if (p.out && p.w_next) {
     const float inv = 1.0f / sqrtf(block_sum(sr, scratch) * inv_h + p.eps);
     TO* o = (TO*)p.out + (size_t)out_row * H;
     for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = Num<TO>::from_f(row[i] * inv * p.w_next[i]);
+  } else if (p.out) {
+    TO* o = (TO*)p.out + (size_t)out_row * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = Num<TO>::from_f(row[i]);
   }
 }
 // The same with the row in registers: row lengths that are multiples of 4 up to 4 x 4 x 1,024, a thread holding up
@@ -158,12 +162,12 @@ norm_chain_vec_kernel(ChainArgs p) {
     sr += sq4(y[g]);
   }
   if (p.out) {
-    const float inv = 1.0f / sqrtf(block_sum(sr, scratch) * inv_h + p.eps);
+    const float inv = p.w_next ? 1.0f / sqrtf(block_sum(sr, scratch) * inv_h + p.eps) : 1.0f;
 #pragma unroll
     for (int g = 0; g < G; ++g) {
       if (!on[g]) continue;
       const int i = 4 * (threadIdx.x + g * blockDim.x);
-      const float4 v = scale4(y[g], inv, p.w_next + i);
+      const float4 v = p.w_next ? scale4(y[g], inv, p.w_next + i) : y[g];
       TO* o = (TO*)p.out + (size_t)out_row * H + i;
       o[0] = Num<TO>::from_f(v.x); o[1] = Num<TO>::from_f(v.y); o[2] = Num<TO>::from_f(v.z); o[3] = Num<TO>::from_f(v.w);
     }
@@ -186,7 +190,7 @@ IFX_API int ifx_norm_chain(const float* a, int a_parts, long long a_stride, cons
                            const float* w_post, float* residual, const float* w_next, void* out, int out_dtype,
                            const int* rows, int n_rows, int hidden, float eps, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
-  if (hidden < 1 || hidden > 49152 || (out && !w_next)) return IFX_ERR_UNSUPPORTED;
+  if (hidden < 1 || hidden > 49152) return IFX_ERR_UNSUPPORTED;
   ChainArgs p{a, a_parts, a_stride, wa, b, b_parts, b_stride, wb, w_post, residual, w_next, out, rows, hidden, eps};
   const uintptr_t ptrs = (uintptr_t)a | (uintptr_t)wa | (uintptr_t)b | (uintptr_t)wb | (uintptr_t)w_post | (uintptr_t)residual |
                          (uintptr_t)w_next;

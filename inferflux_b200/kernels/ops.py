@@ -37,7 +37,7 @@ def _lib():
     global _sigs_done
     lib = library()
     if not _sigs_done:
-        lib.ifx_embed_gather.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+        lib.ifx_embed_gather.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p]
         lib.ifx_add_rmsnorm.argtypes = [c_void_p, c_void_p, c_int, c_int, c_ll, c_void_p, c_float, c_void_p,
                                         c_int, c_void_p, c_int, c_int, c_int, c_void_p]
         lib.ifx_swiglu.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
@@ -159,16 +159,34 @@ def _lib():
         lib.ifx_retention_finish.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_int, c_ll, c_int, c_int, c_int, c_float,
                                              c_void_p]
         lib.ifx_gelu_tanh.argtypes = [c_void_p, c_int, c_ll, c_void_p, c_int, c_ll, c_int, c_int, c_void_p]
-        lib.ifx_moe_route.argtypes = [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]
+        lib.ifx_moe_route.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p]
         lib.ifx_moe_tile_rows.argtypes = [c_int]
         lib.ifx_moe_experts.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                        c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                        c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                         c_void_p]
         lib.ifx_moe_group.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
         lib.ifx_moe_gather_rows.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
         lib.ifx_moe_combine.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
         lib.ifx_gemm_umma_grouped.argtypes = [c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int, c_int,
                                               c_void_p, c_void_p, c_void_p]
+        lib.ifx_activation.argtypes = [c_void_p, c_ll, c_int, c_ll, c_void_p, c_int, c_ll, c_int, c_int, c_int, c_void_p]
+        lib.ifx_causal_conv.argtypes = [c_void_p, c_ll, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                        c_void_p, c_int, c_int, c_void_p, c_ll, c_int, c_int, c_void_p]
+        lib.ifx_ssm_scan.argtypes = [c_void_p, c_ll, c_int, c_int, c_int, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_void_p,
+                                     c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_void_p]
+        lib.ifx_gated_group_norm.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_int, c_ll, c_int, c_int, c_int,
+                                             c_float, c_void_p]
+        lib.ifx_delta_rule_scan.argtypes = [c_void_p, c_ll, c_int, c_int, c_int, c_int, c_void_p, c_ll, c_void_p, c_void_p,
+                                            c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_ll, c_int, c_int, c_int,
+                                            c_float, c_float, c_void_p]
+        lib.ifx_head_norm_gate.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_int, c_ll, c_int, c_int, c_int,
+                                           c_float, c_int, c_void_p]
+        lib.ifx_qkv_norm_rope_write.argtypes = [c_void_p, c_int, c_ll, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
+                                                c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                                c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_void_p]
+        for name in ("ifx_activation", "ifx_causal_conv", "ifx_ssm_scan", "ifx_gated_group_norm", "ifx_delta_rule_scan",
+                     "ifx_head_norm_gate", "ifx_qkv_norm_rope_write"):
+            getattr(lib, name).restype = c_int
         for name in ("ifx_moe_group", "ifx_moe_gather_rows", "ifx_moe_combine", "ifx_gemm_umma_grouped"):
             getattr(lib, name).restype = c_int
         for name in ("ifx_norm_chain", "ifx_conv_rope_kv_write", "ifx_rotate_heads", "ifx_attn_paged_generic_ex",
@@ -223,13 +241,13 @@ def _need(cond: bool, msg: str) -> None:
 
 
 # ------------------------------------------------------------------ elementwise
-def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[t, :] = float32(table[ids[t], :]); ids int32 [N], out float32 [N, H]."""
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """out[t, :] = float32(table[ids[t], :]) * scale; ids int32 [N], out float32 [N, H]."""
     n, (vocab, hidden) = ids.numel(), table.shape
     _need(ids.dtype == torch.int32 and out.dtype == torch.float32, "embed_gather: ids int32, out float32")
     _need(table.is_contiguous() and out.is_contiguous() and tuple(out.shape) == (n, hidden),
           "embed_gather: contiguous table and out [N, H]")
-    _check(_lib().ifx_embed_gather(_ptr(table), _code(table), _ptr(ids), _ptr(out), n, hidden, vocab, _stream()),
+    _check(_lib().ifx_embed_gather(_ptr(table), _code(table), _ptr(ids), _ptr(out), n, hidden, vocab, float(scale), _stream()),
            "embed_gather")
     return out
 
@@ -1163,7 +1181,8 @@ def norm_chain(residual: torch.Tensor, a: Optional[torch.Tensor], eps: float, w_
                w_post: Optional[torch.Tensor] = None, w_next: Optional[torch.Tensor] = None,
                out: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
     """One pass over every row, float32: ``y = a`` (``N(a) * w_a`` with a weight), with ``b`` the mean of the two
-    (normed) branches; ``y = N(y) * w_post`` with a weight; ``residual += y``; ``out = N(residual) * w_next``.
+    (normed) branches; ``y = N(y) * w_post`` with a weight; ``residual += y``; ``out = N(residual) * w_next``
+    (without ``w_next``, ``out`` is the stream itself rounded into its type: for a sublayer that reads the stream as it is).
     ``N(v) = v / sqrt(mean(v^2) + eps)``.  ``a`` and ``b`` are float32 ``[N, H]`` or slices ``[P, N, H]`` that are
     added first.  With ``rows`` (int32) only those rows are computed, into ``out [R, H]``, and the residual is
     left as it is."""
@@ -1177,7 +1196,7 @@ def norm_chain(residual: torch.Tensor, a: Optional[torch.Tensor], eps: float, w_
     ap, a_parts, a_stride = _slices(a, n, hidden, "norm_chain a")
     bp, b_parts, b_stride = _slices(b, n, hidden, "norm_chain b")
     if out is not None:
-        _need(out.is_contiguous() and tuple(out.shape) == (n_rows, hidden) and w_next is not None, "norm_chain: out [rows, H] and w_next")
+        _need(out.is_contiguous() and tuple(out.shape) == (n_rows, hidden), "norm_chain: out [rows, H]")
     _check(_lib().ifx_norm_chain(ap, a_parts, a_stride, _ptr(w_a), bp, b_parts, b_stride, _ptr(w_b), _ptr(w_post),
                                  _ptr(residual), _ptr(w_next), _ptr(out), _code(out) if out is not None else F32,
                                  _ptr(rows), n_rows, hidden, float(eps), _stream()), "norm_chain")
@@ -1354,15 +1373,18 @@ def gelu_tanh(z: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def moe_route(logits: torch.Tensor, top: int):
-    """The ``top`` largest of every row of float32 ``logits [N, E]`` (lowest index first among equals) and the
-    softmax over them alone: (int32 ``[N, top]``, float32 ``[N, top]``)."""
+def moe_route(logits: torch.Tensor, top: int, over_all: bool = False, scale: float = 1.0):
+    """The ``top`` largest of every row of float32 ``logits [N, E]`` (lowest index first among equals) and their
+    weights: the softmax over the chosen logits alone, or, with ``over_all``, the softmax over every expert's
+    logit with the chosen scores divided by their sum (+ 1e-20); either times ``scale``.  Returns (int32
+    ``[N, top]``, float32 ``[N, top]``)."""
     n, experts = logits.shape
     _need(logits.dtype == torch.float32 and logits.is_contiguous(), "moe_route: float32 logits")
     _need(1 <= top <= min(64, experts), f"moe_route: top {top} must be within 1..min(64, experts)")
     chosen = torch.empty((n, top), dtype=torch.int32, device=logits.device)
     weights = torch.empty((n, top), dtype=torch.float32, device=logits.device)
-    _check(_lib().ifx_moe_route(_ptr(logits), n, experts, top, _ptr(chosen), _ptr(weights), _stream()), "moe_route")
+    _check(_lib().ifx_moe_route(_ptr(logits), n, experts, top, int(bool(over_all)), float(scale), _ptr(chosen),
+                                _ptr(weights), _stream()), "moe_route")
     return chosen, weights
 
 
@@ -1373,7 +1395,7 @@ MOE_TENSOR_CORE_PAIRS = 512
 MOE_UMMA_TILE = 256
 
 
-def _moe_experts_umma(x, w_gate_up, w_down, chosen, weights, n, hidden, ff, experts, top) -> torch.Tensor:
+def _moe_experts_umma(x, w_gate_up, w_down, chosen, weights, n, hidden, ff, experts, top, activation) -> torch.Tensor:
     lib, dev, tile = _lib(), x.device, MOE_UMMA_TILE
     pairs = n * top
     max_tiles = pairs // tile + experts
@@ -1387,7 +1409,7 @@ def _moe_experts_umma(x, w_gate_up, w_down, chosen, weights, n, hidden, ff, expe
     _check(lib.ifx_moe_gather_rows(_ptr(x), _code(x), _ptr(sorted_pair), _ptr(xs), rows, hidden, top, _stream()), "moe_gather_rows")
     act = torch.empty((rows, ff), dtype=x.dtype, device=dev)
     flag = error_flag(dev)
-    _check(lib.ifx_gemm_umma_grouped(_ptr(xs), hidden, _ptr(w_gate_up), _ptr(act), ff, BF16, rows, ff, hidden, 1, experts,
+    _check(lib.ifx_gemm_umma_grouped(_ptr(xs), hidden, _ptr(w_gate_up), _ptr(act), ff, BF16, rows, ff, hidden, activation, experts,
                                      _ptr(tile_expert), _ptr(flag), _stream()), "gemm_umma_grouped (gate, up)")
     y = torch.empty((rows, hidden), dtype=torch.float32, device=dev)
     _check(lib.ifx_gemm_umma_grouped(_ptr(act), ff, _ptr(w_down), _ptr(y), hidden, F32, rows, hidden, ff, 0, experts,
@@ -1397,20 +1419,25 @@ def _moe_experts_umma(x, w_gate_up, w_down, chosen, weights, n, hidden, ff, expe
     return out
 
 
+MOE_SWIGLU, MOE_RELU2 = 1, 2
+
+
 def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, chosen: torch.Tensor,
-                weights: torch.Tensor) -> torch.Tensor:
-    """``out[t] = sum_k weights[t, k] * W_down[e] (silu(W_gate[e] x_t) * (W_up[e] x_t))``, ``e = chosen[t, k]``:
-    ``x [N, H]``, ``w_gate_up [E, 2F, H]`` (gate rows, then up rows), ``w_down [E, H, F]`` of one type; float32
-    ``[N, H]`` out.  The pairs are sorted by expert on the device and run as tiles of one expert each."""
+                weights: torch.Tensor, activation: int = MOE_SWIGLU) -> torch.Tensor:
+    """``out[t] = sum_k weights[t, k] * W_down[e] act_e(x_t)``, ``e = chosen[t, k]``.  ``MOE_SWIGLU``: ``w_gate_up
+    [E, 2F, H]`` (gate rows, then up rows) and ``act = silu(W_gate x) * (W_up x)``; ``MOE_RELU2``: ``w_gate_up [E, F, H]``
+    (up rows alone) and ``act = relu(W_up x)^2``.  ``x [N, H]``, ``w_down [E, H, F]`` of one type; float32 ``[N, H]``
+    out.  The pairs are sorted by expert on the device and run as tiles of one expert each."""
     n, hidden = x.shape
-    experts, two_f, _ = w_gate_up.shape
-    ff, top = two_f // 2, chosen.shape[1]
+    experts, up_rows, _ = w_gate_up.shape
+    ff, top = (up_rows // 2 if activation == MOE_SWIGLU else up_rows), chosen.shape[1]
+    _need(activation in (MOE_SWIGLU, MOE_RELU2), "moe_experts: activation")
     _need(x.is_contiguous() and w_gate_up.is_contiguous() and w_down.is_contiguous() and x.dtype == w_gate_up.dtype == w_down.dtype,
           "moe_experts: contiguous operands of one type")
     _need(tuple(w_down.shape) == (experts, hidden, ff) and w_gate_up.shape[2] == hidden, "moe_experts: weight shapes")
     pairs = n * top
     if (MOE_TENSOR_CORES and x.dtype == torch.bfloat16 and pairs >= MOE_TENSOR_CORE_PAIRS and hidden % 8 == 0 and ff % 8 == 0):
-        return _moe_experts_umma(x, w_gate_up, w_down, chosen, weights, n, hidden, ff, experts, top)
+        return _moe_experts_umma(x, w_gate_up, w_down, chosen, weights, n, hidden, ff, experts, top, activation)
     tile = int(_lib().ifx_moe_tile_rows(pairs))
     max_tiles = pairs // tile + experts
     dev = x.device
@@ -1421,8 +1448,172 @@ def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, 
     y = torch.empty((max_tiles * tile, hidden), dtype=torch.float32, device=dev)
     out = torch.empty((n, hidden), dtype=torch.float32, device=dev)
     _check(_lib().ifx_moe_experts(_ptr(x), _code(x), _ptr(w_gate_up), _ptr(w_down), _ptr(chosen), _ptr(weights), n, hidden, ff,
-                                  experts, top, tile, max_tiles, _ptr(tile_expert), _ptr(sorted_pair), _ptr(pair_row),
+                                  experts, top, activation, tile, max_tiles, _ptr(tile_expert), _ptr(sorted_pair), _ptr(pair_row),
                                   _ptr(act), _ptr(y), _ptr(out), _stream()), "moe_experts")
     global launch_count
     launch_count += 3
     return out
+
+
+# ------------------------------------------------- activations, state-space scan, delta rule, normed q/k/v
+ACT_GELU, ACT_TANH, ACT_RELU2, ACT_SILU, ACT_SIGMOID = 0, 1, 2, 3, 4
+
+
+def activation(z: torch.Tensor, out: torch.Tensor, act: int) -> torch.Tensor:
+    """``out = act(z)`` element by element, computed in float32 and rounded once: ``z`` float32 rows ``[M, C]`` (a view
+    with any row stride) or contiguous slices ``[P, M, C]`` that are added first; ``out`` rows of either type.
+    ``act``: ``ACT_GELU`` (tanh form), ``ACT_TANH``, ``ACT_RELU2`` (the square of relu), ``ACT_SILU``, ``ACT_SIGMOID``."""
+    m, cols = out.shape
+    _need(z.dtype == torch.float32 and z.stride(-1) == 1 and out.stride(1) == 1, "activation: float32 sums, rows out")
+    if z.dim() == 3:
+        _need(z.is_contiguous() and tuple(z.shape[1:]) == (m, cols), "activation: slices [P, M, C]")
+        parts, pstride, zstride = z.shape[0], m * cols, cols
+    else:
+        _need(tuple(z.shape) == (m, cols), "activation: [M, C]")
+        parts, pstride, zstride = 1, 0, z.stride(0)
+    _check(_lib().ifx_activation(_ptr(z), zstride, parts, pstride, _ptr(out), _code(out), out.stride(0), m, cols, int(act),
+                                 _stream()), "activation")
+    return out
+
+
+def causal_conv(x: torch.Tensor, col0: int, channels: int, w: torch.Tensor, bias: Optional[torch.Tensor],
+                tail: Optional[torch.Tensor], row_entry: torch.Tensor, entry_q_start: torch.Tensor,
+                entry_q_len: torch.Tensor, entry_slot: torch.Tensor, n_entries: int, out: torch.Tensor,
+                silu: bool = True) -> torch.Tensor:
+    """``out[t, c] = act(bias[c] + sum_j w[c, j] * u_(t - taps + 1 + j)[c])`` with ``u = x[:, col0 + c]`` over the
+    tokens of one sequence and ``u = 0`` ahead of its first token: ``x`` float32 rows, ``w`` float32 ``[channels,
+    taps]``, ``out`` float32 ``[N, channels]``.  The ``taps - 1`` inputs before the step's first row come from
+    ``tail [slots, taps - 1, channels]``, which a second launch then brings up to date."""
+    n, taps = x.shape[0], w.shape[1]
+    _need(x.dtype == torch.float32 and x.dim() == 2 and x.stride(1) == 1 and col0 + channels <= x.shape[1],
+          "causal_conv: float32 rows")
+    _need(w.dtype == torch.float32 and w.is_contiguous() and w.shape[0] == channels, "causal_conv: w float32 [channels, taps]")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == channels), "causal_conv: bias float32 [channels]")
+    _need(out.dtype == torch.float32 and out.stride(1) == 1 and tuple(out.shape) == (n, channels), "causal_conv: out")
+    if taps > 1:
+        _need(tail is not None and tail.dtype == torch.float32 and tail.is_contiguous()
+              and tuple(tail.shape[1:]) == (taps - 1, channels), "causal_conv: tail float32 [slots, taps - 1, channels]")
+    _check(_lib().ifx_causal_conv(_ptr(x), x.stride(0), col0, _ptr(w), _ptr(bias), taps, _ptr(tail) if taps > 1 else None,
+                                  _ptr(row_entry), _ptr(entry_q_start), _ptr(entry_q_len), _ptr(entry_slot), n, n_entries,
+                                  _ptr(out), out.stride(0), channels, 1 if silu else 0, _stream()), "causal_conv")
+    if taps > 1:
+        global launch_count
+        launch_count += 1
+    return out
+
+
+def ssm_scan(xbc: torch.Tensor, x_col: int, b_col: int, c_col: int, dt: torch.Tensor, dt_bias: torch.Tensor,
+             a_log: torch.Tensor, d_skip: torch.Tensor, state: torch.Tensor, entry_q_start: torch.Tensor,
+             entry_q_len: torch.Tensor, entry_slot: torch.Tensor, n_entries: int, out: torch.Tensor, heads: int,
+             groups: int, vdim: int, n_state: int) -> torch.Tensor:
+    """The selective state-space recurrence, float32.  Per head ``h`` with ``B``, ``C`` of group ``h // (heads /
+    groups)``: ``dt = softplus(dt_raw + dt_bias)``, ``S <- exp(-exp(a_log) dt) S + dt B x^T``, ``y = S^T C + D x``.
+    ``xbc`` float32 rows hold x (``heads * vdim`` from ``x_col``), B and C (``groups * n_state`` from ``b_col``,
+    ``c_col``); ``dt`` float32 rows ``[N, heads]`` (a view); ``state [slots, heads, vdim, n_state]`` is read at an
+    entry's start and written at its end; ``out`` float32 ``[N, heads * vdim]``."""
+    n = xbc.shape[0]
+    _need(xbc.dtype == torch.float32 and xbc.stride(1) == 1 and dt.dtype == torch.float32 and dt.stride(1) == 1
+          and tuple(dt.shape) == (n, heads), "ssm_scan: float32 rows")
+    _need(all(v.dtype == torch.float32 and v.numel() == heads and v.is_contiguous() for v in (dt_bias, a_log, d_skip)),
+          "ssm_scan: dt_bias, a_log, d float32 [heads]")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, vdim, n_state),
+          "ssm_scan: state float32 [slots, heads, vdim, state]")
+    _need(out.dtype == torch.float32 and out.stride(1) == 1 and tuple(out.shape) == (n, heads * vdim), "ssm_scan: out")
+    _check(_lib().ifx_ssm_scan(_ptr(xbc), xbc.stride(0), x_col, b_col, c_col, _ptr(dt), dt.stride(0), _ptr(dt_bias),
+                               _ptr(a_log), _ptr(d_skip), _ptr(state), _ptr(entry_q_start), _ptr(entry_q_len),
+                               _ptr(entry_slot), n_entries, _ptr(out), out.stride(0), heads, groups, vdim, n_state,
+                               _stream()), "ssm_scan")
+    return out
+
+
+def gated_group_norm(y: torch.Tensor, z: torch.Tensor, w: torch.Tensor, out: torch.Tensor, groups: int, eps: float) -> torch.Tensor:
+    """``v = y * silu(z)``; every one of ``groups`` equal parts of a row of ``v`` is divided by its own root mean
+    square (eps inside the root) and multiplied by ``w``: ``y``, ``z`` float32 rows (views), ``w`` float32 ``[C]``."""
+    n, cols = y.shape
+    _need(y.dtype == torch.float32 and z.dtype == torch.float32 and y.stride(1) == 1 and z.stride(1) == 1
+          and tuple(z.shape) == (n, cols) and cols % groups == 0, "gated_group_norm: float32 rows, groups dividing them")
+    _need(w.dtype == torch.float32 and w.numel() == cols and w.is_contiguous() and out.stride(1) == 1
+          and tuple(out.shape) == (n, cols), "gated_group_norm: w float32 [C], out [N, C]")
+    _check(_lib().ifx_gated_group_norm(_ptr(y), y.stride(0), _ptr(z), z.stride(0), _ptr(w), _ptr(out), _code(out),
+                                       out.stride(0), n, groups, cols // groups, float(eps), _stream()), "gated_group_norm")
+    return out
+
+
+def delta_rule_scan(proj: torch.Tensor, r_col: int, k_col: int, v_col: int, a_col: int, w_raw: torch.Tensor,
+                    w0: torch.Tensor, a_bias: torch.Tensor, state: torch.Tensor, entry_q_start: torch.Tensor,
+                    entry_q_len: torch.Tensor, entry_slot: torch.Tensor, n_entries: int, out: torch.Tensor, heads: int,
+                    dim: int, vdim: int, decay_scale: float, key_eps: float) -> torch.Tensor:
+    """The generalized delta rule, float32.  Per head: ``w = exp(-decay_scale * sigmoid(w_raw + w0))``, ``a =
+    sigmoid(a_raw + a_bias)``, ``u = k / sqrt(sum(k^2) + key_eps)``, ``S <- diag(w) S - (a * u)(u^T S) + k v^T``
+    (both terms from the old state), ``o = S^T r``.  ``proj`` float32 rows hold r, k, a_raw (``heads * dim`` each)
+    and v (``heads * vdim``) from the given columns; ``w_raw`` float32 rows ``[N, heads * dim]``;
+    ``state [slots, heads, vdim, dim]``; ``out`` float32 ``[N, heads * vdim]``."""
+    n = proj.shape[0]
+    _need(proj.dtype == torch.float32 and proj.stride(1) == 1 and w_raw.dtype == torch.float32 and w_raw.stride(1) == 1
+          and tuple(w_raw.shape) == (n, heads * dim), "delta_rule_scan: float32 rows")
+    _need(all(v.dtype == torch.float32 and v.numel() == heads * dim and v.is_contiguous() for v in (w0, a_bias)),
+          "delta_rule_scan: w0 and a_bias float32 [heads * dim]")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, vdim, dim),
+          "delta_rule_scan: state float32 [slots, heads, vdim, dim]")
+    _need(out.dtype == torch.float32 and out.stride(1) == 1 and tuple(out.shape) == (n, heads * vdim), "delta_rule_scan: out")
+    _check(_lib().ifx_delta_rule_scan(_ptr(proj), proj.stride(0), r_col, k_col, v_col, a_col, _ptr(w_raw), w_raw.stride(0),
+                                      _ptr(w0), _ptr(a_bias), _ptr(state), _ptr(entry_q_start), _ptr(entry_q_len),
+                                      _ptr(entry_slot), n_entries, _ptr(out), out.stride(0), heads, dim, vdim,
+                                      float(decay_scale), float(key_eps), _stream()), "delta_rule_scan")
+    return out
+
+
+GATE_NONE, GATE_SIGMOID, GATE_SILU = 0, 1, 2
+
+
+def head_norm_gate(o: torch.Tensor, gate: Optional[torch.Tensor], w: Optional[torch.Tensor], out: torch.Tensor, heads: int,
+                   vdim: int, eps: float, gate_kind: int = GATE_SIGMOID) -> torch.Tensor:
+    """``out[t, h] = o[t, h] / sqrt(mean(o[t, h]^2) + eps) * w[h] * g(gate[t, h])`` with ``g`` sigmoid, silu or
+    absent: ``o``, ``gate`` float32 rows (views), ``w`` float32 ``[heads * vdim]`` or None, ``out`` rows of either type."""
+    n = o.shape[0]
+    _need(o.dtype == torch.float32 and o.stride(1) == 1 and tuple(o.shape) == (n, heads * vdim) and out.stride(1) == 1
+          and tuple(out.shape) == (n, heads * vdim), "head_norm_gate: o float32 [N, heads * vdim], out alike")
+    _need(gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1 and tuple(gate.shape) == tuple(o.shape)),
+          "head_norm_gate: gate float32 rows")
+    _need(w is None or (w.dtype == torch.float32 and w.is_contiguous() and w.numel() == heads * vdim), "head_norm_gate: w")
+    _check(_lib().ifx_head_norm_gate(_ptr(o), o.stride(0), _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(w),
+                                     _ptr(out), _code(out), out.stride(0), n, heads, vdim, float(eps),
+                                     int(gate_kind) if gate is not None else GATE_NONE, _stream()), "head_norm_gate")
+    return out
+
+
+MIX_NONE, MIX_STORE, MIX_BLEND = 0, 1, 2
+
+
+def qkv_norm_rope_write(proj: torch.Tensor, wq: Optional[torch.Tensor], wk: Optional[torch.Tensor], eps: float,
+                        cos: torch.Tensor, sin: torch.Tensor, layout: int, n_heads: int, n_kv: int, dim: int, vdim: int,
+                        v_norm: bool, mix_mode: int, mix_lambda: Optional[torch.Tensor], v_first: Optional[torch.Tensor],
+                        q_out: torch.Tensor, slot_map: torch.Tensor, k_layer: torch.Tensor, v_layer: torch.Tensor,
+                        page_stride: int, page_size: int) -> None:
+    """The first ``(n_heads + n_kv) * dim + n_kv * vdim`` columns of the float32 projection ``proj [N, W]`` (or
+    slices ``[P, N, W]``) are q, k and v heads side by side.  With ``wq`` (``wk``) all query (key) columns of a token
+    are divided by their common root mean square (eps inside the root) and multiplied by that weight; q and k heads
+    are rotated by ``cos``/``sin`` ``[N, r/2]``; with ``v_norm`` every value head is divided by its own root mean
+    square; ``MIX_STORE`` keeps the values in ``v_first [N, n_kv * vdim]``, ``MIX_BLEND`` replaces them by
+    ``(1 - lambda) v + lambda v_first``.  q goes to ``q_out``, k and v into the paged cache at ``slot_map``."""
+    n = q_out.shape[0]
+    channels = (n_heads + n_kv) * dim + n_kv * vdim
+    width = proj.shape[-1]
+    _need(proj.dtype == torch.float32 and proj.is_contiguous() and width >= channels, "qkv_norm_rope: float32 projection")
+    parts, pstride = (proj.shape[0], n * width) if proj.dim() == 3 else (1, 0)
+    _need(wq is None or (wq.dtype == torch.float32 and wq.is_contiguous() and wq.numel() == n_heads * dim), "qkv_norm_rope: wq")
+    _need(wk is None or (wk.dtype == torch.float32 and wk.is_contiguous() and wk.numel() == n_kv * dim), "qkv_norm_rope: wk")
+    _need(cos.dtype == torch.float32 and cos.is_contiguous() and sin.is_contiguous() and cos.shape == sin.shape
+          and cos.shape[0] == n, "qkv_norm_rope: cos/sin float32 [N, r/2]")
+    _need(q_out.is_contiguous() and tuple(q_out.shape) == (n, n_heads * dim) and k_layer.dtype == q_out.dtype,
+          "qkv_norm_rope: q_out [N, heads * dim] of the cache's type")
+    if mix_mode != MIX_NONE:
+        _need(v_first is not None and v_first.dtype == torch.float32 and v_first.is_contiguous()
+              and tuple(v_first.shape) == (n, n_kv * vdim), "qkv_norm_rope: v_first float32 [N, kv_heads * vdim]")
+    if mix_mode == MIX_BLEND:
+        _need(mix_lambda is not None and mix_lambda.dtype == torch.float32 and mix_lambda.numel() == 1, "qkv_norm_rope: lambda")
+    _check(_lib().ifx_qkv_norm_rope_write(_ptr(proj), parts, pstride, width, _ptr(wq), _ptr(wk), float(eps), _ptr(cos),
+                                          _ptr(sin), cos.shape[1], layout, n_heads, n_kv, dim, vdim, int(bool(v_norm)),
+                                          int(mix_mode), _ptr(mix_lambda), _ptr(v_first), _ptr(q_out), _code(q_out),
+                                          _ptr(slot_map), _ptr(k_layer), _ptr(v_layer), page_stride, page_size, n,
+                                          _stream()), "qkv_norm_rope_write")

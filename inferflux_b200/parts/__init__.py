@@ -16,6 +16,8 @@ from .junction import LoopEntry
 from .window_attention import WindowAttention
 from .retention import Retention
 from .side_by_side import SideBySide
+from .state_space import Mamba2
+from .delta_rule import GeneralDelta
 
 __all__ = ["Part", "KVNeed", "StateNeed", "RunInfo", "Linear", "RMSNorm", "RotaryHalf",
            "GQAttention", "SwiGLU", "PreNormBlock", "TokenEmbedding", "LinearHead", "LayerNorm", "PolyNormFF",

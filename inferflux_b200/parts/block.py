@@ -23,6 +23,7 @@ from ..config.registry import register_part
 from ..kernels import ops
 from .base import NormedDelta, PartialSums, RunInfo
 from .linear import Linear
+from .norm import normed_sum
 
 
 class PreNormBlock:
@@ -191,6 +192,57 @@ class PrePostNormBlock:
         return NormedDelta(self.ff.forward(x2, ctx), self.ff_post.weight, self.ff_post.eps)
 
 
+class PostNormBlock:
+    """A norm behind every sublayer and none ahead: the sublayers read the stream itself,
+
+        residual += norm_1(mixer(residual))
+        residual += norm_2(feed_forward(residual))                  (a layer may have no feed-forward)
+
+    A sublayer's result is not added here: it goes on as a :class:`NormedDelta` with the weight of the norm
+    behind it.  The next reader of the stream (this block's feed-forward, the next block's mixer, or the model's
+    last norm) norms it and adds it to the float32 stream in one kernel, which also hands out the stream rounded
+    into the engine's type for the sublayer's products (a float32 engine reads the stream in place)."""
+
+    family = "arrangement"
+    roles = {"mixer": "mixer", "mixer_post_norm": "norm", "feed_forward": "feed_forward", "feed_forward_post_norm": "norm"}
+    optional_roles = frozenset({"feed_forward", "feed_forward_post_norm"})
+
+    def __init__(self, parts: Dict[str, object], position_name: Optional[str]):
+        self.mixer, self.mixer_post = parts["mixer"], parts["mixer_post_norm"]
+        self.ff, self.ff_post = parts.get("feed_forward"), parts.get("feed_forward_post_norm")
+        if (self.ff is None) != (self.ff_post is None):
+            raise ValueError("a post_norm block has a feed-forward with the norm behind it or neither")
+        self.position_name = position_name
+
+    @staticmethod
+    def _read(residual: torch.Tensor, delta, ctx) -> torch.Tensor:
+        """Adds the pending delta into the stream and returns what a sublayer reads: the stream in the engine's type."""
+        if ctx.dtype == torch.float32:
+            if isinstance(delta, NormedDelta):
+                normed_sum(residual, delta, None, None)
+            elif delta is not None:
+                d, n = (delta.tensor, delta.count) if isinstance(delta, PartialSums) else (delta, 1)
+                ops.add_into(residual, d, n)
+            return residual
+        out = torch.empty(residual.shape, dtype=ctx.dtype, device=residual.device)
+        if isinstance(delta, NormedDelta):
+            return normed_sum(residual, delta, None, out)
+        if delta is not None:
+            d, n = (delta.tensor, delta.count) if isinstance(delta, PartialSums) else (delta, 1)
+            ops.add_into(residual, d, n)
+        return ops.convert(residual, out)
+
+    def forward(self, residual: torch.Tensor, delta, ctx, run: RunInfo):
+        x = self._read(residual, delta, ctx)
+        position = ctx.position_tables.get(self.position_name) if self.position_name else None
+        a = NormedDelta(self.mixer.forward(x, ctx, run, position), self.mixer_post.weight, self.mixer_post.eps)
+        if self.ff is None:
+            return a
+        x2 = self._read(residual, a, ctx)
+        return NormedDelta(self.ff.forward(x2, ctx), self.ff_post.weight, self.ff_post.eps)
+
+
 register_part("arrangement", "pre_post_norm", PrePostNormBlock)
+register_part("arrangement", "post_norm", PostNormBlock)
 register_part("arrangement", "parallel", ParallelBlock)
 register_part("arrangement", "junction", JunctionBlock)

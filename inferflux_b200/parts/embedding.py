@@ -22,13 +22,15 @@ from .linear import Linear
 
 
 class TokenEmbedding(Part):
-    """params: ``vocab``, ``hidden``, ``name`` (weight ``<name>.weight``) or ``weight_name`` (the table's full name)."""
+    """params: ``vocab``, ``hidden``, ``name`` (weight ``<name>.weight``) or ``weight_name`` (the table's full name),
+    ``scale`` (default 1: the float32 row is multiplied by it)."""
 
     family = "embedding"
 
     def __init__(self, params, prefix, dtype, device):
         super().__init__(params, prefix, dtype, device)
         self.vocab, self.hidden = int(params["vocab"]), int(params["hidden"])
+        self.scale = float(params.get("scale", 1.0))
         self.table: torch.Tensor = None
 
     @classmethod
@@ -45,7 +47,7 @@ class TokenEmbedding(Part):
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
         out = torch.empty((token_ids.numel(), self.hidden), dtype=torch.float32, device=token_ids.device)
-        return ops.embed_gather(self.table, token_ids, out)
+        return ops.embed_gather(self.table, token_ids, out, self.scale)
 
     def forward_step(self, ctx) -> torch.Tensor:
         return self.forward(ctx.token_ids)

@@ -147,17 +147,52 @@ class GeluMLP(Part):
         return self.down.forward(act, out_dtype=torch.float32, allow_partials=True, f32_sums=True)
 
 
+class SquaredReluMLP(Part):
+    """``down( relu(up(x))^2 )``, no biases.  The up projection leaves float32 sums; the activation rounds once into
+    the engine's type.  params: ``hidden``, ``intermediate``, ``name`` (tensors ``<prefix>.<name>.{up,down}``)."""
+
+    family = "feed_forward"
+
+    def __init__(self, params, prefix, dtype, device):
+        super().__init__(params, prefix, dtype, device)
+        self.hidden, self.intermediate = int(params["hidden"]), int(params["intermediate"])
+        self.up: Linear = None
+        self.down: Linear = None
+
+    @classmethod
+    def weight_specs(cls, params: Dict[str, Any], prefix: str) -> List[WeightSpec]:
+        h, i = int(params["hidden"]), int(params["intermediate"])
+        n = lambda leaf: cls.full_name(prefix, params, leaf)
+        return [WeightSpec(n("up"), (i, h), MATRIX), WeightSpec(n("down"), (h, i), MATRIX)]
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        n = lambda leaf: self.full_name(self.prefix, self.params, leaf)
+        self.up, self.down = Linear(tensors.pop(n("up"))), Linear(tensors.pop(n("down")))
+
+    def forward(self, x: torch.Tensor, ctx):
+        z = self.up.forward(x, out_dtype=torch.float32, allow_partials=True, f32_sums=True)
+        act = torch.empty((x.shape[0], self.intermediate), dtype=x.dtype, device=x.device)
+        ops.activation(z.tensor if isinstance(z, PartialSums) else z, act, ops.ACT_RELU2)
+        return self.down.forward(act, out_dtype=torch.float32, allow_partials=True, f32_sums=True)
+
+
 class RoutedExperts(Part):
     """A mixture of experts: every token runs the ``top`` experts with the largest router logits and adds their
-    results, weighted by the softmax over the chosen logits alone.
+    results, weighted.
 
-        z = W_router x + b            float32 (x may be the engine type's rounding)
-        expert e: W_down_e ( silu(W_gate_e x) * (W_up_e x) ),  no biases
+        z = W_router x (+ b)          float32 (x may be the engine type's rounding)
+        ``route`` ``chosen``:  weights = softmax over the chosen logits alone
+        ``route`` ``all``:     s = softmax(z) over every expert; weights = the chosen s over their sum (+ 1e-20)
+        either times ``scale``
+        expert e, ``activation`` ``swiglu``:  W_down_e ( silu(W_gate_e x) * (W_up_e x) )
+                  ``activation`` ``relu2``:   W_down_e ( relu(W_up_e x)^2 )                      no biases
+        ``shared`` (an intermediate size): one more expert of the ``relu2`` form that every token runs, added unweighted
 
     The experts' matrices are stacked at load; the (token, expert) pairs are sorted by expert on the device and
     run as tiles of one expert each, so nothing waits for the host and a step of single tokens is captured like
-    any other.  params: ``hidden``, ``intermediate`` (of one expert), ``experts``, ``top``, ``name`` (tensors
-    ``<prefix>.<name>.router``, ``.router.b``, ``.e<i>.{gate,up,down}``)."""
+    any other.  params: ``hidden``, ``intermediate`` (of one expert), ``experts``, ``top``, ``activation``, ``route``,
+    ``scale``, ``router_bias`` (default true), ``shared``, ``name`` (tensors ``<prefix>.<name>.router``, ``.router.b``,
+    ``.e<i>.{gate,up,down}``, ``.shared.{up,down}``)."""
 
     family = "feed_forward"
 
@@ -167,40 +202,72 @@ class RoutedExperts(Part):
         self.experts, self.top = int(params["experts"]), int(params["top"])
         if not 1 <= self.top <= min(self.experts, 64):
             raise ValueError(f"routed_experts: top {self.top} must be within 1..min(experts, 64)")
+        self.activation = {"swiglu": ops.MOE_SWIGLU, "relu2": ops.MOE_RELU2}.get(params.get("activation", "swiglu"))
+        self.over_all = {"chosen": False, "all": True}.get(params.get("route", "chosen"))
+        if self.activation is None or self.over_all is None:
+            raise ValueError("routed_experts: activation is 'swiglu' or 'relu2', route is 'chosen' or 'all'")
+        self.scale = float(params.get("scale", 1.0))
+        self.shared = self._shared(params, prefix, dtype, device)
         self.router: Linear = None
         self.gate_up: torch.Tensor = None
         self.down: torch.Tensor = None
 
     @classmethod
+    def _shared(cls, params, prefix, dtype=None, device=None):
+        """The shared expert as a part of its own (or its class and parameters, for the weight list)."""
+        if not params.get("shared"):
+            return None
+        sp = dict(name=cls.full_name("", params, "shared"), hidden=int(params["hidden"]), intermediate=int(params["shared"]))
+        return SquaredReluMLP(sp, prefix, dtype, device) if dtype is not None else sp
+
+    def subparts(self) -> list:
+        return [self.shared] if self.shared is not None else []
+
+    @classmethod
     def weight_specs(cls, params: Dict[str, Any], prefix: str) -> List[WeightSpec]:
         h, i, e = int(params["hidden"]), int(params["intermediate"]), int(params["experts"])
         n = lambda leaf: cls.full_name(prefix, params, leaf)
-        specs = [WeightSpec(n("router"), (e, h), MATRIX, std=0.5), WeightSpec(n("router.b"), (e,), VECTOR, std=0.5)]
+        specs = [WeightSpec(n("router"), (e, h), MATRIX, std=0.5)]
+        if params.get("router_bias", True):
+            specs.append(WeightSpec(n("router.b"), (e,), VECTOR, std=0.5))
+        mats = ("gate", "up") if params.get("activation", "swiglu") == "swiglu" else ("up",)
         for k in range(e):
-            specs += [WeightSpec(n(f"e{k}.gate"), (i, h), MATRIX), WeightSpec(n(f"e{k}.up"), (i, h), MATRIX),
-                      WeightSpec(n(f"e{k}.down"), (h, i), MATRIX)]
+            specs += [WeightSpec(n(f"e{k}.{x}"), (i, h), MATRIX) for x in mats] + [WeightSpec(n(f"e{k}.down"), (h, i), MATRIX)]
+        sp = cls._shared(params, prefix)
+        if sp is not None:
+            specs += SquaredReluMLP.weight_specs(sp, prefix)
         return specs
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         n = lambda leaf: self.full_name(self.prefix, self.params, leaf)
         # The router's products are 32-bit whatever the engine: a bfloat16 weight times a bfloat16 input is exact
         # in float32, and the sums are float32 (the library's product or the weight-streaming kernel).
-        self.router = Linear(tensors.pop(n("router")), tensors.pop(n("router.b")))
-        mats = [[tensors.pop(n(f"e{k}.{x}")) for x in ("gate", "up", "down")] for k in range(self.experts)]
+        self.router = Linear(tensors.pop(n("router")), tensors.pop(n("router.b")) if self.params.get("router_bias", True) else None)
+        ups = ("gate", "up") if self.activation == ops.MOE_SWIGLU else ("up",)
+        mats = [[tensors.pop(n(f"e{k}.{x}")) for x in (*ups, "down")] for k in range(self.experts)]
         kinds = {m.dtype for row in mats for m in row}
         cast = (lambda m: m.float()) if len(kinds) > 1 else (lambda m: m)
-        self.gate_up = torch.stack([torch.cat([cast(g), cast(u)], dim=0) for g, u, _ in mats]).contiguous()
-        self.down = torch.stack([cast(d) for _, _, d in mats]).contiguous()
+        self.gate_up = torch.stack([torch.cat([cast(m) for m in row[:-1]], dim=0) for row in mats]).contiguous()
+        self.down = torch.stack([cast(row[-1]) for row in mats]).contiguous()
+        if self.shared is not None:
+            self.shared.load(tensors)
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         logits = self.router.forward(x, out_dtype=torch.float32)
-        chosen, weights = ops.moe_route(logits, self.top)
+        chosen, weights = ops.moe_route(logits, self.top, self.over_all, self.scale)
+        xe = x
         if x.dtype != self.gate_up.dtype:
-            x = ops.convert(x.contiguous(), torch.empty(x.shape, dtype=self.gate_up.dtype, device=x.device))
-        return ops.moe_experts(x.contiguous(), self.gate_up, self.down, chosen, weights)
+            xe = ops.convert(x.contiguous(), torch.empty(x.shape, dtype=self.gate_up.dtype, device=x.device))
+        out = ops.moe_experts(xe.contiguous(), self.gate_up, self.down, chosen, weights, self.activation)
+        if self.shared is not None:
+            y = self.shared.forward(x, ctx)
+            y, parts = (y.tensor, y.count) if isinstance(y, PartialSums) else (y, 1)
+            ops.add_into(out, y, parts)
+        return out
 
 
 register_part("feed_forward", "swiglu", SwiGLU)
 register_part("feed_forward", "gelu_mlp", GeluMLP)
 register_part("feed_forward", "routed_experts", RoutedExperts)
+register_part("feed_forward", "relu2_mlp", SquaredReluMLP)
 register_part("feed_forward", "polynorm", PolyNormFF)

@@ -33,6 +33,8 @@ def scaled_frequencies(rotary_dim: int, theta: float, scaling: Optional[dict]):
     freq = torch.pow(torch.tensor(theta, dtype=torch.float64), -2.0 * i / max(rotary_dim, 1))
     if not scaling:
         return freq, 1.0
+    if "low" in scaling:
+        return banded_frequencies(freq, scaling), 1.0
     factor, original = float(scaling["factor"]), float(scaling["original"])
     fast, slow = float(scaling["fast"]), float(scaling["slow"])
     where = lambda t: rotary_dim * math.log(original / (2.0 * math.pi * t)) / (2.0 * math.log(theta))
@@ -42,9 +44,23 @@ def scaled_frequencies(rotary_dim: int, theta: float, scaling: Optional[dict]):
     return freq / factor * ramp + freq * (1.0 - ramp), 0.1 * math.log(factor) + 1.0
 
 
+def banded_frequencies(freq: torch.Tensor, scaling: dict) -> torch.Tensor:
+    """Frequency scaling by wavelength bands, ``scaling`` = {factor, low, high, original}: with the wavelength
+    ``l = 2 pi / f``, a frequency stays where ``l < original / high``, becomes ``f / factor`` where ``l > original /
+    low``, and in between, with ``s = (original / l - low) / (high - low)``, becomes ``(1 - s) f / factor + s f``.
+    cos and sin keep their size."""
+    factor, low, high, original = (float(scaling[k]) for k in ("factor", "low", "high", "original"))
+    wavelength = 2.0 * math.pi / freq
+    s = (original / wavelength - low) / (high - low)
+    mid = (1.0 - s) * freq / factor + s * freq
+    out = torch.where(wavelength > original / low, freq / factor, mid)
+    return torch.where(wavelength < original / high, freq, out)
+
+
 class RotaryHalf(Part):
-    """params: ``rotary_dim`` (how many leading dims of a head rotate), ``theta``, ``scaling`` (None, or
-    {factor, original, fast, slow}: see :func:`scaled_frequencies`).  The table it makes is one cosine and one
+    """params: ``rotary_dim`` (how many leading dims of a head rotate), ``theta``, ``scaling`` (None,
+    {factor, original, fast, slow}: see :func:`scaled_frequencies`, or {factor, low, high, original}: see
+    :func:`banded_frequencies`).  The table it makes is one cosine and one
     sine per token and pair; how a mixer pairs the dimensions (halves or neighbours) is the mixer's business."""
 
     family = "position"

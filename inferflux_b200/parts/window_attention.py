@@ -4,6 +4,13 @@ decoder designs, each a parameter:
   q, k, v (and a gate g) = one stacked projection of the normed input, float32 sums
   ``conv`` taps          a short causal convolution over time on every channel of q, k and v, straight after
                          the projection: y_t = sum_j w[:, j] u_(t - taps + 1 + j), with u = 0 ahead of the first token
+  ``qk_norm``            all of a token's query columns (heads side by side) are divided by their common root
+                         mean square and multiplied by a weight of that size; the key columns likewise; ahead
+                         of the rotation
+  ``v_norm``             every value head is divided by its own root mean square (no weight); cached so
+  ``v_mix``              ``first``: this layer's (normed) values are kept for the step's later layers;
+                         ``blend``: v <- (1 - lambda) v + lambda v_first with the kept values of the same token
+                         and lambda a stored number; the blended values are what is cached
   rotation               of the first ``rot_dims`` dimensions of every query and key head by the layer's
                          position table, pairs ``interleaved`` (2i, 2i+1) or in ``half``s (i, i + rot_dims/2)
   scores                 s = (q . k) * scale, then ``softcap`` * tanh(s / softcap) if given
@@ -75,8 +82,10 @@ def describe_query_tiles(layout, put) -> QueryTiles:
 class WindowAttention(Part):
     """params: ``hidden``, ``heads``, ``kv_heads``, ``dim``, ``vdim``, ``conv`` (taps, 0 = none), ``rot_dims``,
     ``rot_layout`` (``interleaved`` or ``half``), ``scale`` (None = ``dim^-1/2``), ``softcap`` (None = none),
-    ``window`` (None = all keys), ``keep_first``, ``sink``, ``gate``, ``name``.  Tensors
-    ``<prefix>.<name>.{q,k,v,g,o}`` and ``<prefix>.<name>.{q,k,v}.conv`` ``[channels, taps]``.
+    ``window`` (None = all keys), ``keep_first``, ``sink``, ``gate``, ``qk_norm``, ``v_norm``, ``v_mix`` (None,
+    ``first`` or ``blend``), ``eps`` (of these norms), ``name``.  Tensors ``<prefix>.<name>.{q,k,v,g,o}``,
+    ``<prefix>.<name>.{q,k,v}.conv`` ``[channels, taps]``, ``<prefix>.<name>.{q,k}.norm`` and ``<prefix>.<name>.vmix``
+    (one number; stored but unused in the ``first`` layer).
     State: ``conv_tail`` float32 ``[taps - 1, channels of q, k and v]``.
     Position: a pair ``(cos, sin)`` of float32 ``[N, rot_dims / 2]`` tensors."""
 
@@ -99,6 +108,15 @@ class WindowAttention(Part):
         self.window = int(p.get("window") or 0)
         self.keep_first = int(p.get("keep_first") or 0) if self.window else 0
         self.sink, self.gate = bool(p.get("sink")), bool(p.get("gate"))
+        self.qk_norm, self.v_norm, self.v_mix = bool(p.get("qk_norm")), bool(p.get("v_norm")), p.get("v_mix") or None
+        self.eps = float(p.get("eps") or 0.0)
+        if self.v_mix not in (None, "first", "blend"):
+            raise ValueError(f"v_mix {self.v_mix!r} is not one of None, 'first', 'blend'")
+        self.normed = self.qk_norm or self.v_norm or self.v_mix is not None
+        if self.normed and self.taps:
+            raise ValueError("window_attention: the short convolution and the norms of q, k, v are not built together")
+        if self.normed and self.eps <= 0.0:
+            raise ValueError("window_attention: norms of q, k or v need a positive eps")
         if self.heads % self.kv_heads:
             raise ValueError(f"heads {self.heads} is not a multiple of kv_heads {self.kv_heads}")
         if self.rot_dims % 2 or self.rot_dims > self.dim:
@@ -109,6 +127,7 @@ class WindowAttention(Part):
             raise ValueError("a convolution of more than 16 taps is not built")
         self.qkvg: Linear = None
         self.conv_w: Optional[torch.Tensor] = None
+        self.q_norm_w = self.k_norm_w = self.mix_lambda = None
         self.o: Linear = None
 
     @classmethod
@@ -126,6 +145,11 @@ class WindowAttention(Part):
             specs += [WeightSpec(n(f"{x}.conv"), (r, taps), VECTOR, std=0.5) for x, r in rows.items()]
         if params.get("gate"):
             specs.append(WeightSpec(n("g"), (nh * vd, h), MATRIX))
+        if params.get("qk_norm"):
+            specs += [WeightSpec(n("q.norm"), (nh * d,), VECTOR, init="one_plus_normal"),
+                      WeightSpec(n("k.norm"), (nkv * d,), VECTOR, init="one_plus_normal")]
+        if params.get("v_mix"):
+            specs.append(WeightSpec(n("vmix"), (), VECTOR, std=0.3))
         specs.append(WeightSpec(n("o"), (h, nh * vd), MATRIX))
         return specs
 
@@ -150,6 +174,11 @@ class WindowAttention(Part):
         del mats
         if self.taps >= 1:
             self.conv_w = torch.cat([tensors.pop(n(f"{x}.conv")).float() for x in ("q", "k", "v")]).contiguous()
+        if self.qk_norm:
+            self.q_norm_w = tensors.pop(n("q.norm")).to(torch.float32).contiguous()
+            self.k_norm_w = tensors.pop(n("k.norm")).to(torch.float32).contiguous()
+        if self.v_mix:
+            self.mix_lambda = tensors.pop(n("vmix")).to(torch.float32).reshape(1).contiguous()
         self.o = Linear(tensors.pop(n("o")))
 
     def describe_step(self, layout, put) -> QueryTiles:
@@ -175,10 +204,24 @@ class WindowAttention(Part):
         k_layer, v_layer = views["k"], views["v"]
         proj = self.qkvg.forward(x, out_dtype=torch.float32)            # float32 sums: they go on into the convolution and the rotation
         q = torch.empty((n, self.heads * self.dim), dtype=x.dtype, device=x.device)
-        ops.conv_rope_kv_write(proj, self.conv_w, self.taps, run.states["conv_tail"] if self.taps > 1 else None,
-                               step.row_entry, ctx.entry_q_start, ctx.entry_q_len, ctx.entry_slot, ctx.n_entries, cos, sin,
-                               self.layout, self.heads, self.kv_heads, self.dim, self.vdim, q, ctx.slot_maps[g],
-                               k_layer, v_layer, page_stride, ctx.page_size)
+        if self.normed:
+            mode, v_first = ops.MIX_NONE, None
+            if self.v_mix == "first":
+                mode = ops.MIX_STORE
+                v_first = ctx.scratch["v_first"] = torch.empty((n, self.kv_heads * self.vdim), dtype=torch.float32, device=x.device)
+            elif self.v_mix == "blend":
+                mode, v_first = ops.MIX_BLEND, ctx.scratch.get("v_first")
+                if v_first is None or tuple(v_first.shape) != (n, self.kv_heads * self.vdim):
+                    raise RuntimeError("window_attention: v_mix 'blend' needs an earlier layer of the step with v_mix 'first' "
+                                       "and the same kv_heads and vdim")
+            ops.qkv_norm_rope_write(proj, self.q_norm_w, self.k_norm_w, self.eps, cos, sin, self.layout, self.heads,
+                                    self.kv_heads, self.dim, self.vdim, self.v_norm, mode, self.mix_lambda, v_first, q,
+                                    ctx.slot_maps[g], k_layer, v_layer, page_stride, ctx.page_size)
+        else:
+            ops.conv_rope_kv_write(proj, self.conv_w, self.taps, run.states["conv_tail"] if self.taps > 1 else None,
+                                   step.row_entry, ctx.entry_q_start, ctx.entry_q_len, ctx.entry_slot, ctx.n_entries, cos, sin,
+                                   self.layout, self.heads, self.kv_heads, self.dim, self.vdim, q, ctx.slot_maps[g],
+                                   k_layer, v_layer, page_stride, ctx.page_size)
         if out is None:
             out = torch.empty((n, self.heads * self.vdim), dtype=x.dtype, device=x.device)
         gate = proj[:, self._channels(self.params):] if self.gate else None

@@ -35,6 +35,9 @@ class WeightSpec:
     embedding).
     init: how the random-weights mode fills it: ``normal`` N(0, std) or
     ``one_plus_normal`` 1 + N(0, std).
+    A dimension given as -1 is one that no configuration key names: the stored
+    tensor's own size stands (the part reads it at load); random weights take
+    ``free_size`` there.
     """
 
     name: str
@@ -43,6 +46,10 @@ class WeightSpec:
     optional: bool = False
     init: str = "normal"
     std: float = 0.02
+    free_size: int = 16
+
+    def fits(self, shape) -> bool:
+        return len(shape) == len(self.shape) and all(w == -1 or int(g) == int(w) for g, w in zip(shape, self.shape))
 
 
 class WeightsError(ValueError):
@@ -98,7 +105,7 @@ def load_weights(folder: str, specs: Iterable[WeightSpec], engine_dtype: torch.d
         for s in specs:
             if s.name in where and s.kind != IGNORED:
                 dtype, shape = where[s.name].info(s.name)
-                if tuple(shape) != tuple(s.shape):
+                if not s.fits(tuple(shape)):
                     wrong_shape.append((s.name, tuple(shape), tuple(s.shape)))
                 is_float = dtype.is_floating_point
                 if (s.kind == TABLE) == is_float:

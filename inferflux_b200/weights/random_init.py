@@ -34,10 +34,11 @@ def random_tensors(specs: Iterable[WeightSpec], seed: int, dtype: torch.dtype = 
             continue
         gen = torch.Generator(device=device)
         gen.manual_seed(_seed_for(seed, s.name))
+        shape = tuple(s.free_size if d == -1 else d for d in s.shape)
         if s.kind == TABLE:
-            out[s.name] = torch.zeros(s.shape, dtype=torch.int32, device=device)
+            out[s.name] = torch.zeros(shape, dtype=torch.int32, device=device)
             continue
-        t = torch.randn(s.shape, generator=gen, dtype=torch.float32, device=device) * s.std
+        t = torch.randn(shape, generator=gen, dtype=torch.float32, device=device) * s.std
         if s.init == "one_plus_normal":
             t += 1.0
         store = (vector_dtype or dtype) if s.kind == VECTOR else dtype

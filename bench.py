@@ -203,10 +203,30 @@ def pemorax_config(size: str, layers: int):
                         for i in range(layers)])
 
 
+def tekosun_config(size: str, layers: int):
+    """A Tekosun config.json at the widths of one of the family sizes above: layers in turn a state-space mixer (an
+    inner width of twice the model's in heads of 64, a state of 128, 8 groups, four taps), the generalized delta rule
+    (heads of 64 across the model's width) and two of attention (the family's heads and kv heads of 128, a window of
+    1,024, band-scaled rotary positions, value mixing); every layer with 16 squared-relu experts of a quarter of the
+    family's feed-forward width of which a token takes 4, and a shared expert of that width."""
+    _, hidden, heads, kv_heads, inter, vocab, _ = SIZES[size]
+    ff = inter // 4 // 8 * 8
+    moe = dict(kind="moe", expert=dict(ff=ff), router=dict(experts=16, top=4, scale=2.5), shared=dict(ff=ff))
+    attn = dict(type="attention", mlp=moe, mixer=dict(
+        heads=heads, kv_heads=kv_heads, dim=128, vdim=128, scale=128 ** -0.5, v_mix=True, mask=dict(size=1024),
+        rot=dict(dims=128, base=500000.0, scaling=dict(factor=8.0, low=1.0, high=4.0, original=8192))))
+    ssm = dict(type="mamba2", mlp=moe, mixer=dict(heads=2 * hidden // 64, vdim=64, state=128, groups=8, conv=4, norm_groups=1))
+    delta = dict(type="general_delta", mlp=moe, mixer=dict(heads=hidden // 64, dim=64))
+    turn = [ssm, delta, attn, attn]
+    return dict(architecture="Tekosun", width=hidden, vocab=vocab, norm=dict(eps=1e-6), embedding=dict(scale=float(hidden) ** 0.5),
+                layers=[turn[i % 4] for i in range(layers)])
+
+
 def architecture_workload(args) -> int:
-    """--arch kunonex / pemorax: prefill (one 2,048-token prompt) and decode (batch 8 at the given context) of a
-    model of that design beside a Qwen2 model of the same width, layer count, feed-forward width and vocabulary,
-    both with random bfloat16 weights, device-timed with CUDA events after warm-up.  One JSON line."""
+    """--arch kunonex / pemorax / tekosun: prefill (one 2,048-token prompt) and decode (batch 8 at the given context)
+    of a model of that design beside a model of the same width, layer count and vocabulary (Qwen2 with the same
+    feed-forward width; for tekosun the closest design, Pemorax), both with random bfloat16 weights, device-timed
+    with CUDA events after warm-up.  One JSON line."""
     import torch
     from inferflux_b200 import Engine, SamplingParams, StepEntry
     layers = args.layers or 8
@@ -214,14 +234,15 @@ def architecture_workload(args) -> int:
     warmup = max(3, args.warmup)
     greedy = SamplingParams(temperature=0.0, max_tokens=1 << 30, ignore_eos=True)
     arch = args.arch
-    design = {"kunonex": kunonex_config, "pemorax": pemorax_config}[arch]
-    out = {"metric": f"prefill and decode tokens/s, {arch.capitalize()} beside Qwen2 at the {args.size.upper()} widths", "impl": "ours",
+    design = {"kunonex": kunonex_config, "pemorax": pemorax_config, "tekosun": tekosun_config}[arch]
+    beside = "pemorax" if arch == "tekosun" else "qwen2"
+    beside_cfg = pemorax_config(args.size, layers) if arch == "tekosun" else dict(family_config(args.size), num_hidden_layers=layers)
+    out = {"metric": f"prefill and decode tokens/s, {arch.capitalize()} beside {beside.capitalize()} at the {args.size.upper()} widths", "impl": "ours",
            "n_gpus": 1, "dtype": "bf16", "data": "synthetic: seeded random weights, uniform random token ids",
            "steps": args.steps, "warmup": warmup,
            "config": {"layers": layers, "size": args.size, "global_batch": batch, "seq_len": ctx, "prefill_tokens": T,
                       "l2": "weights and cache exceed L2; no flush"}}
-    for name, cfgd in ((arch, design(args.size, layers)),
-                       ("qwen2", dict(family_config(args.size), num_hidden_layers=layers))):
+    for name, cfgd in ((arch, design(args.size, layers)), (beside, beside_cfg)):
         vocab = cfgd.get("vocab") or cfgd["vocab_size"]
         eng = Engine.from_config(cfgd, seed=0, dtype="bfloat16", kv_cache_tokens=batch * (ctx + 64) + T, max_seqs=batch + 1,
                                  max_batch_tokens=4096, max_batch_size=batch, chunked_prefill_tokens=2048,
@@ -288,12 +309,12 @@ def main() -> int:
     ap.add_argument("--mixed", type=int, default=0, metavar="N",
                     help="instead of the decode step: N requests with prompts of 128 to 2,048 tokens and 256 output "
                          "tokens each through Engine.generate (chunked prompts beside decoding requests)")
-    ap.add_argument("--arch", default="qwen2", choices=["qwen2", "kunonex", "pemorax"],
-                    help="kunonex or pemorax: instead of the default workload, a model of that design beside a Qwen2 model "
-                         "of equal size (--size, --layers, default 8), prefill and decode")
+    ap.add_argument("--arch", default="qwen2", choices=["qwen2", "kunonex", "pemorax", "tekosun"],
+                    help="kunonex, pemorax or tekosun: instead of the default workload, a model of that design beside a model "
+                         "of equal size (Qwen2; for tekosun, Pemorax) (--size, --layers, default 8), prefill and decode")
     args = ap.parse_args()
 
-    if args.arch in ("kunonex", "pemorax") and args.impl == "ours":
+    if args.arch in ("kunonex", "pemorax", "tekosun") and args.impl == "ours":
         return architecture_workload(args)
     if args.impl == "reference":
         return reference_arm()

@@ -279,3 +279,79 @@ def make_pemorax_folder(cfg: dict, seed: int, folder: Optional[str] = None, **kw
 
 
 load_plain_folder = load_kunonex_plain        # (config dict, float64 tensors) of any model folder
+
+
+# ------------------------------------------------------------------ Tekosun
+_BANDS = dict(factor=4.0, low=1.0, high=8.0, original=64)
+_TK_MOE = lambda ff, experts, top, scale=None, shared=None: dict(
+    kind="moe", expert=dict(ff=ff), router={k: v for k, v in (("experts", experts), ("top", top), ("scale", scale)) if v is not None},
+    **({"shared": dict(ff=shared)} if shared else {}))
+# Tiny Tekosun configurations that differ in every size, option and order of layers.  A: attention first (it keeps its
+# values for the later one, whose heads and key size differ), part of a head rotates by banded frequencies, windows of
+# 20 and 33, a layer without feed-forward, one state-space group, a shared expert here and none there.
+TK_A = dict(architecture="Tekosun", width=64, vocab=300, norm=dict(eps=1e-5), embedding=dict(scale=3.0), layers=[
+    dict(type="attention", mixer=dict(heads=4, kv_heads=2, dim=16, vdim=24, scale=0.6, v_mix=True, mask=dict(size=20),
+                                      rot=dict(dims=8, base=10000.0, scaling=_BANDS)), mlp=_TK_MOE(40, 5, 2, 1.7, 24)),
+    dict(type="mamba2", mixer=dict(heads=3, vdim=12, state=8, groups=1, conv=4, norm_groups=1), mlp=None),
+    dict(type="general_delta", mixer=dict(heads=2, dim=12), mlp=_TK_MOE(32, 4, 1, 0.5)),
+    dict(type="attention", mixer=dict(heads=2, kv_heads=2, dim=32, vdim=24, scale=0.4, v_mix=True, mask=dict(size=33),
+                                      rot=dict(dims=32, base=300.0)), mlp=_TK_MOE(40, 5, 2, 2.5, 56))])
+# B: sizes that are no multiple of 4 or 8 anywhere, two state-space groups and two norm groups, two taps, an attention
+# without window, rotation, value mixing or key/value head count, a window shorter than a page, every expert chosen,
+# no embedding scale, a decay projection of five
+TK_B = dict(architecture="Tekosun", width=50, vocab=77, norm=dict(eps=3e-6), layers=[
+    dict(type="general_delta", mixer=dict(heads=3, dim=10, decay_rank=5), mlp=_TK_MOE(35, 3, 3, shared=9)),
+    dict(type="attention", mixer=dict(heads=3, dim=10, scale=0.9), mlp=None),
+    dict(type="mamba2", mixer=dict(heads=4, vdim=5, state=6, groups=2, conv=2, norm_groups=2), mlp=_TK_MOE(18, 3, 1, 3.0)),
+    dict(type="attention", mixer=dict(heads=5, kv_heads=1, dim=6, vdim=10, scale=1.2, mask=dict(size=7), rot=dict(dims=2, base=20.0)),
+         mlp=_TK_MOE(18, 3, 2, shared=30)),
+    dict(type="mamba2", mixer=dict(heads=2, vdim=7, state=3, conv=1), mlp=None)])
+# C: heads of 64 (the sizes tensor-core kernels take), a state of 64 and of more rows than a thread holds, a window
+# longer than several pages, many experts, three attention layers of which two blend, four norm groups
+TK_C = dict(architecture="Tekosun", width=128, vocab=200, norm=dict(eps=1e-6), embedding=dict(scale=11.0), layers=[
+    dict(type="mamba2", mixer=dict(heads=4, vdim=32, state=64, groups=2, conv=4, norm_groups=4), mlp=_TK_MOE(48, 12, 3, 2.0, 64)),
+    dict(type="attention", mixer=dict(heads=4, kv_heads=2, dim=64, vdim=64, scale=0.25, v_mix=True, mask=dict(size=70),
+                                      rot=dict(dims=64, base=200000.0, scaling=_BANDS)), mlp=_TK_MOE(48, 12, 3, 2.0, 64)),
+    dict(type="general_delta", mixer=dict(heads=2, dim=64), mlp=None),
+    dict(type="attention", mixer=dict(heads=2, kv_heads=2, dim=32, vdim=64, scale=0.3, v_mix=True, rot=dict(dims=16, base=1e4)),
+         mlp=_TK_MOE(24, 6, 2, 1.0)),
+    dict(type="attention", mixer=dict(heads=4, kv_heads=2, dim=64, vdim=64, scale=0.25, v_mix=True, mask=dict(size=70),
+                                      rot=dict(dims=64, base=200000.0, scaling=_BANDS)), mlp=None)])
+TK = {"A": TK_A, "B": TK_B, "C": TK_C}
+
+
+def tekosun_tensors(cfg: dict, seed: int, sharpen: float = 1.0):
+    """Random tensors (bfloat16 matrices) for a Tekosun configuration.  Queries and keys are normed, so how peaked the
+    softmax is lies with the configuration's ``scale``; ``sharpen`` multiplies the query norm's weight on top.  The
+    projections that feed the recurrences are enlarged so that states carry weight, and the state-space decays are
+    slowed (``A_log`` lowered) so that a state lost many tokens back would show."""
+    from inferflux_b200.config import load_config
+    from inferflux_b200.config.registry import build_spec
+    from inferflux_b200.engine.model import Model
+    from inferflux_b200.weights.random_init import random_tensors
+    config = load_config(json.loads(json.dumps(cfg)))
+    specs = Model(build_spec(config), torch.float32, "cpu").weight_specs()
+    tensors = random_tensors(specs, seed, torch.bfloat16, None, "cpu")
+    for name in tensors:
+        f, add = 1.0, 0.0
+        if name.endswith(".q.norm"):
+            f = sharpen
+        elif name.endswith((".mix.in", ".mix.r", ".mix.k", ".mix.v", ".mix.a", ".mix.g", ".mix.w1", ".up", ".down", ".mix.o")):
+            f = 5.0
+        elif name.endswith(".A_log"):
+            add = -2.0
+        elif name == "embed":
+            f = 20.0
+        if f != 1.0 or add:
+            tensors[name] = (tensors[name].float() * f + add).to(tensors[name].dtype)
+    return config, tensors
+
+
+def make_tekosun_folder(cfg: dict, seed: int, folder: Optional[str] = None, **kw) -> str:
+    from inferflux_b200.weights.safetensors_io import write_safetensors
+    folder = folder or tempfile.mkdtemp(prefix="ifx_tk_")
+    config, tensors = tekosun_tensors(cfg, seed, **kw)
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    write_safetensors(os.path.join(folder, "model.safetensors"), tensors)
+    return folder

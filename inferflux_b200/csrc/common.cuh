@@ -126,6 +126,20 @@ __device__ __forceinline__ void pdl_enter() {
   pdl_launch_dependents();
   pdl_wait();
 }
+// Asynchronous copies of single floats (or four at a time) from global into shared memory (a scan stages the next tokens' rows while it
+// works through the present ones): the copies of a thread up to cp_async_commit() form a group, cp_async_wait_all()
+// waits for all of the thread's groups; a __syncthreads() after it makes every thread's copies visible to the block.
+__device__ __forceinline__ void cp_async_f32(float* dst_shared, const float* src_global) {
+  const unsigned dst = (unsigned)__cvta_generic_to_shared(dst_shared);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(dst), "l"(src_global) : "memory");
+}
+__device__ __forceinline__ void cp_async_f32x4(float* dst_shared, const float* src_global) {   // both 16-byte aligned
+  const unsigned dst = (unsigned)__cvta_generic_to_shared(dst_shared);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src_global) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;\n" ::: "memory"); }
+
 template <typename Kern, typename... Args>
 inline int launch_pdl(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
   cudaLaunchConfig_t cfg = {};

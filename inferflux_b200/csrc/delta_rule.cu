@@ -8,19 +8,22 @@
 //   o_t = S_t^T r_t
 //
 // The scan runs a block per (head, entry, block of value columns); a thread owns one value column and every LN-th
-// key row of it (R rows in registers).  A token costs one reduction over the key rows for u^T S, the update, and a
-// second reduction for the output.  Tokens are staged through shared memory TC at a time, where the decay, the
-// removal rate and the unit key are computed once per block.  The state of a sequence lives in its slot as
-// [heads][vdim][dim] float32, read at the start of an entry and written at its end, so a prompt may be cut
+// fourth group of four key rows of it (R rows in registers, read from shared memory 16 bytes at a time).  A token costs one reduction over the key rows for u^T S, the update, and a
+// second reduction for the output; the sums run in four chains so that no addition waits on the one before it.
+// Tokens are staged through shared memory a chunk at a time in two buffers: while the block works through one
+// chunk, asynchronous copies bring the next chunk's rows, and between chunks a warp a token turns the raw numbers
+// into the decay, the unit key and the removal rate times the unit key.  The state of a sequence lives in its slot
+// as [heads][vdim][dim] float32, read at the start of an entry and written at its end, so a prompt may be cut
 // anywhere and a decoded token is the same kernel with one token.
 //
 // The finish brings every head's output to unit root mean square, multiplies by a weight over all heads and by
 // sigmoid(gate), and rounds once into the engine's type.
 #include "common.cuh"
+#include <cstdlib>
 
 namespace {
 constexpr int R = 16;           // key rows a thread holds
-constexpr int TC = 8;           // tokens staged at a time
+constexpr int MAX_TC = 16;      // tokens staged at a time at most
 
 struct DeltaArgs {
   const float* proj; long long stride; int r_col, k_col, v_col, a_col;   // float32 rows: r, k, v heads and raw removal rates
@@ -29,20 +32,17 @@ struct DeltaArgs {
   float* state;                                                          // [slots][heads][vdim][dim]
   const int* entry_q_start; const int* entry_q_len; const int* entry_slot;
   float* out; long long out_stride;                                      // [row][heads * vdim]
-  int heads, dim, vdim, ln, cols_per_block;
+  int heads, dim, vdim, cols_per_block, tc, vec;    // vec: every staged row starts 16-byte aligned
   float decay_scale, key_eps;
 };
 
-__global__ void __launch_bounds__(1024)
+template <int LN>
+__global__ void __launch_bounds__(512)
 delta_rule_scan_kernel(DeltaArgs p) {
-  extern __shared__ float sm[];
-  const int LN = p.ln, NP = R * LN, PB = p.cols_per_block;
-  float* rs = sm;                       // [TC][NP]
-  float* ks = rs + TC * NP;             // [TC][NP]
-  float* us = ks + TC * NP;             // [TC][NP]  unit key
-  float* ws = us + TC * NP;             // [TC][NP]  decay
-  float* as = ws + TC * NP;             // [TC][NP]  removal rate times unit key
-  float* vs = as + TC * NP;             // [TC][PB]
+  extern __shared__ __align__(16) float sm[];
+  constexpr int NP = R * LN;
+  const int PB = p.cols_per_block, TC = p.tc;
+  const int BUF = (TC * (5 * NP + PB) + 3) & ~3;   // per buffer (16-byte aligned): r, k, unit key, decay, removal rate [TC][NP] each, v [TC][PB]
   pdl_enter();
   const int h = blockIdx.x, e = blockIdx.y, p0 = blockIdx.z * PB;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
@@ -52,69 +52,142 @@ delta_rule_scan_kernel(DeltaArgs p) {
   const int r0 = p.entry_q_start[e], len = p.entry_q_len[e];
   const int hd = h * p.dim;
   float* st = p.state + (((size_t)p.entry_slot[e] * p.heads + h) * p.vdim + (valid ? col : 0)) * p.dim;
-  float S[R];
+  float S[R];                              // S[4 j + c] is key row 4 (j LN + ln) + c: a 16-byte load per four rows
 #pragma unroll
   for (int i = 0; i < R; ++i) {
-    const int n = i * LN + ln;
+    const int n = 4 * ((i >> 2) * LN + ln) + (i & 3);
     S[i] = (valid && n < p.dim) ? st[n] : 0.0f;
   }
-  for (int t0 = 0; t0 < len; t0 += TC) {
+  // the raw rows of the tokens from t0 on, asked for; rows past the head's size are zeros
+  auto stage = [&](int t0, float* buf) {
     const int nt = min(TC, len - t0);
-    __syncthreads();
-    for (int idx = tid; idx < nt * NP; idx += blockDim.x) {
-      const int tt = idx / NP, n = idx - tt * NP;
-      const size_t row = (size_t)(r0 + t0 + tt);
-      const bool on = n < p.dim;
-      const float* pr = p.proj + row * p.stride;
-      rs[idx] = on ? pr[p.r_col + hd + n] : 0.0f;
-      ks[idx] = on ? pr[p.k_col + hd + n] : 0.0f;
-      const float wr = on ? p.wraw[row * p.w_stride + hd + n] + p.w0[hd + n] : 0.0f;
-      ws[idx] = on ? expf(-p.decay_scale / (1.0f + expf(-wr))) : 0.0f;
-      const float ar = on ? pr[p.a_col + hd + n] + p.ab[hd + n] : 0.0f;
-      as[idx] = on ? 1.0f / (1.0f + expf(-ar)) : 0.0f;
+    float* rs = buf; float* ks = rs + TC * NP; float* ws = ks + 2 * TC * NP; float* as = ws + TC * NP; float* vs = as + TC * NP;
+    if (p.vec) {
+      for (int idx = tid; idx < nt * (NP / 4); idx += blockDim.x) {
+        const int tt = idx / (NP / 4), n = 4 * (idx - tt * (NP / 4)), at = tt * NP + n;
+        const size_t row = (size_t)(r0 + t0 + tt);
+        if (n < p.dim) {
+          const float* pr = p.proj + row * p.stride + hd + n;
+          cp_async_f32x4(rs + at, pr + p.r_col);
+          cp_async_f32x4(ks + at, pr + p.k_col);
+          cp_async_f32x4(as + at, pr + p.a_col);
+          cp_async_f32x4(ws + at, p.wraw + row * p.w_stride + hd + n);
+        } else {
+          const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+          *reinterpret_cast<float4*>(rs + at) = *reinterpret_cast<float4*>(ks + at) = zero;
+          *reinterpret_cast<float4*>(as + at) = *reinterpret_cast<float4*>(ws + at) = zero;
+        }
+      }
+      const int pq = PB >> 2;
+      for (int idx = tid; idx < nt * pq; idx += blockDim.x) {
+        const int tt = idx / pq, c = 4 * (idx - tt * pq);
+        if (p0 + c < p.vdim) cp_async_f32x4(vs + tt * PB + c, p.proj + (size_t)(r0 + t0 + tt) * p.stride + p.v_col + h * p.vdim + p0 + c);
+        else *reinterpret_cast<float4*>(vs + tt * PB + c) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      }
+    } else {
+      for (int idx = tid; idx < nt * NP; idx += blockDim.x) {
+        const int tt = idx / NP, n = idx - tt * NP;
+        const size_t row = (size_t)(r0 + t0 + tt);
+        if (n < p.dim) {
+          const float* pr = p.proj + row * p.stride + hd + n;
+          cp_async_f32(rs + idx, pr + p.r_col);
+          cp_async_f32(ks + idx, pr + p.k_col);
+          cp_async_f32(as + idx, pr + p.a_col);
+          cp_async_f32(ws + idx, p.wraw + row * p.w_stride + hd + n);
+        } else {
+          rs[idx] = ks[idx] = as[idx] = ws[idx] = 0.0f;
+        }
+      }
+      for (int idx = tid; idx < nt * PB; idx += blockDim.x) {
+        const int tt = idx / PB, c = idx - tt * PB;
+        if (p0 + c < p.vdim) cp_async_f32(vs + idx, p.proj + (size_t)(r0 + t0 + tt) * p.stride + p.v_col + h * p.vdim + p0 + c);
+        else vs[idx] = 0.0f;
+      }
     }
-    for (int idx = tid; idx < nt * PB; idx += blockDim.x) {
-      const int tt = idx / PB, c = idx - tt * PB;
-      vs[idx] = p0 + c < p.vdim ? p.proj[(size_t)(r0 + t0 + tt) * p.stride + p.v_col + h * p.vdim + p0 + c] : 0.0f;
-    }
-    __syncthreads();
-    for (int tt = warp; tt < nt; tt += nwarps) {            // the unit key: a warp a token, a fixed order of additions
+    cp_async_commit();
+  };
+  // once the copies are in: a warp a token, the unit key (a fixed order of additions), the decay, the removal rate
+  auto prepare = [&](int nt, float* buf) {
+    float* ks = buf + TC * NP; float* us = ks + TC * NP; float* ws = us + TC * NP; float* as = ws + TC * NP;
+    for (int tt = warp; tt < nt; tt += nwarps) {
       float ss = 0.0f;
       for (int n = lane; n < NP; n += 32) ss = fmaf(ks[tt * NP + n], ks[tt * NP + n], ss);
       ss = warp_sum(ss);
       const float inv = 1.0f / sqrtf(ss + p.key_eps);
       for (int n = lane; n < NP; n += 32) {
-        const float u = ks[tt * NP + n] * inv;
-        us[tt * NP + n] = u;
-        as[tt * NP + n] *= u;
+        const int i = tt * NP + n;
+        const float u = ks[i] * inv;
+        us[i] = u;
+        if (n < p.dim) {
+          ws[i] = expf(-p.decay_scale / (1.0f + expf(-(ws[i] + p.w0[hd + n]))));
+          as[i] = u / (1.0f + expf(-(as[i] + p.ab[hd + n])));
+        }
       }
     }
+  };
+  if (len > 0) {
+    stage(0, sm);
+    cp_async_wait_all();
     __syncthreads();
+    prepare(min(TC, len), sm);
+    __syncthreads();
+  }
+  int which = 0;
+  for (int t0 = 0; t0 < len; t0 += TC, which ^= 1) {
+    const int nt = min(TC, len - t0);
+    const bool more = t0 + TC < len;
+    float* cur = sm + which * BUF;
+    float* nxt = sm + (which ^ 1) * BUF;          // last read two chunks ago, before the barriers of the last turn
+    if (more) stage(t0 + TC, nxt);
+    const float* rs = cur; const float* ks = rs + TC * NP; const float* us = ks + TC * NP; const float* ws = us + TC * NP;
+    const float* as = ws + TC * NP; const float* vs = as + TC * NP;
+#pragma unroll 2
     for (int tt = 0; tt < nt; ++tt) {
-      const float* u = us + tt * NP + ln;
-      const float* w = ws + tt * NP + ln;
-      const float* au = as + tt * NP + ln;
-      const float* k = ks + tt * NP + ln;
-      const float* r = rs + tt * NP + ln;
+      const float4* u4 = reinterpret_cast<const float4*>(us + tt * NP) + ln;
+      const float4* w4 = reinterpret_cast<const float4*>(ws + tt * NP) + ln;
+      const float4* a4 = reinterpret_cast<const float4*>(as + tt * NP) + ln;
+      const float4* k4 = reinterpret_cast<const float4*>(ks + tt * NP) + ln;
+      const float4* r4 = reinterpret_cast<const float4*>(rs + tt * NP) + ln;
       const float v = pl < PB ? vs[tt * PB + pl] : 0.0f;
-      float dot = 0.0f;
+      float d0 = 0.0f, d1 = 0.0f, d2 = 0.0f, d3 = 0.0f;
 #pragma unroll
-      for (int i = 0; i < R; ++i) dot = fmaf(u[i * LN], S[i], dot);
-      for (int o = LN >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-      float y = 0.0f;
-#pragma unroll
-      for (int i = 0; i < R; ++i) {
-        S[i] = fmaf(w[i * LN], S[i], fmaf(k[i * LN], v, -au[i * LN] * dot));
-        y = fmaf(S[i], r[i * LN], y);
+      for (int j = 0; j < R / 4; ++j) {
+        const float4 u = u4[j * LN];
+        d0 = fmaf(u.x, S[4 * j], d0);
+        d1 = fmaf(u.y, S[4 * j + 1], d1);
+        d2 = fmaf(u.z, S[4 * j + 2], d2);
+        d3 = fmaf(u.w, S[4 * j + 3], d3);
       }
-      for (int o = LN >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-      if (valid && ln == 0) p.out[(size_t)(r0 + t0 + tt) * p.out_stride + h * p.vdim + col] = y;
+      float dot = (d0 + d1) + (d2 + d3);
+      for (int o = LN >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+      float y0 = 0.0f, y1 = 0.0f, y2 = 0.0f, y3 = 0.0f;
+#pragma unroll
+      for (int j = 0; j < R / 4; ++j) {
+        const float4 w = w4[j * LN], k = k4[j * LN], au = a4[j * LN], r = r4[j * LN];
+        S[4 * j] = fmaf(w.x, S[4 * j], fmaf(k.x, v, -au.x * dot));
+        S[4 * j + 1] = fmaf(w.y, S[4 * j + 1], fmaf(k.y, v, -au.y * dot));
+        S[4 * j + 2] = fmaf(w.z, S[4 * j + 2], fmaf(k.z, v, -au.z * dot));
+        S[4 * j + 3] = fmaf(w.w, S[4 * j + 3], fmaf(k.w, v, -au.w * dot));
+        y0 = fmaf(S[4 * j], r.x, y0);
+        y1 = fmaf(S[4 * j + 1], r.y, y1);
+        y2 = fmaf(S[4 * j + 2], r.z, y2);
+        y3 = fmaf(S[4 * j + 3], r.w, y3);
+      }
+      float yo = (y0 + y1) + (y2 + y3);
+      for (int o = LN >> 1; o > 0; o >>= 1) yo += __shfl_xor_sync(0xffffffffu, yo, o);
+      if (valid && ln == 0) p.out[(size_t)(r0 + t0 + tt) * p.out_stride + h * p.vdim + col] = yo;
+    }
+    if (more) {
+      cp_async_wait_all();
+      __syncthreads();
+      prepare(min(TC, len - t0 - TC), nxt);
+      __syncthreads();
     }
   }
   if (valid) {
 #pragma unroll
     for (int i = 0; i < R; ++i) {
-      const int n = i * LN + ln;
+      const int n = 4 * ((i >> 2) * LN + ln) + (i & 3);
       if (n < p.dim) st[n] = S[i];
     }
   }
@@ -154,23 +227,37 @@ IFX_API int ifx_delta_rule_scan(const float* proj, long long stride, int r_col, 
                                 const float* wraw, long long w_stride, const float* w0, const float* ab, float* state,
                                 const int* entry_q_start, const int* entry_q_len, const int* entry_slot, int n_entries,
                                 float* out, long long out_stride, int heads, int dim, int vdim, float decay_scale,
-                                float key_eps, cudaStream_t stream) {
+                                float key_eps, int n_rows, cudaStream_t stream) {
   if (n_entries <= 0) return 0;
   if (heads < 1 || dim < 1 || dim > R * 32 || vdim < 1 || n_entries > 65535) return IFX_ERR_UNSUPPORTED;
   int ln = 1;
   while (R * ln < dim) ln <<= 1;
   int pb = 256 / ln;                      // blocks of at most 256 threads: more blocks to spread over the SMs
   if (pb > vdim) pb = vdim;
-  if (pb > 16 && heads * n_entries * ((vdim + pb - 1) / pb) < 148) pb = 16;
+  // single tokens: small blocks, to spread the states over the SMs; portions: large ones, which stage and prepare
+  // a token's rows once for all their columns
+  if (const char* force = getenv("IFX_TRY_PB_DELTA")) pb = atoi(force) < pb ? atoi(force) : pb; else
+  if (pb > 16 && n_rows <= 4 * n_entries && heads * n_entries * ((vdim + pb - 1) / pb) < 148) pb = 16;
   const int threads = (pb * ln + 31) / 32 * 32;
+  int tc = n_rows <= n_entries ? 1 : MAX_TC;
+  while (tc > 1 && (size_t)2 * (tc * (5 * R * ln + pb) + 3) * sizeof(float) > 96 * 1024) tc >>= 1;
+  const int vec = !((dim | vdim | pb | r_col | k_col | v_col | a_col) & 3) && !((stride | w_stride) & 3) &&
+                  !(((uintptr_t)proj | (uintptr_t)wraw) & 15);
   DeltaArgs p{proj, stride, r_col, k_col, v_col, a_col, wraw, w_stride, w0, ab, state, entry_q_start, entry_q_len, entry_slot,
-              out, out_stride, heads, dim, vdim, ln, pb, decay_scale, key_eps};
-  const size_t smem = (size_t)TC * (5 * R * ln + pb) * sizeof(float);
-  if (smem > 48 * 1024) {
-    cudaError_t err = cudaFuncSetAttribute(delta_rule_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (err != cudaSuccess) return (int)err;
-  }
-  const int rc = launch_pdl(delta_rule_scan_kernel, dim3(heads, n_entries, (vdim + pb - 1) / pb), dim3(threads), smem, stream, p);
+              out, out_stride, heads, dim, vdim, pb, tc, vec, decay_scale, key_eps};
+  const size_t smem = (size_t)2 * (tc * (5 * R * ln + pb) + 3) * sizeof(float);
+  const dim3 grid(heads, n_entries, (vdim + pb - 1) / pb), block(threads);
+  int rc = IFX_ERR_UNSUPPORTED;
+#define IFX_DELTA_CASE(L)                                                                                           \
+  case L: {                                                                                                         \
+    if (smem > 48 * 1024) {                                                                                         \
+      cudaError_t err = cudaFuncSetAttribute(delta_rule_scan_kernel<L>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      if (err != cudaSuccess) return (int)err;                                                                      \
+    }                                                                                                               \
+    rc = launch_pdl(delta_rule_scan_kernel<L>, grid, block, smem, stream, p);                                       \
+  } break;
+  switch (ln) { IFX_DELTA_CASE(1) IFX_DELTA_CASE(2) IFX_DELTA_CASE(4) IFX_DELTA_CASE(8) IFX_DELTA_CASE(16) IFX_DELTA_CASE(32) }
+#undef IFX_DELTA_CASE
   return rc ? rc : IFX_LAUNCH_CHECK();
 }
 

@@ -9,16 +9,18 @@
 //                          y_t  = S_t^T C_t + D[h] x_t
 //
 // The scan runs a block per (entry, head, block of value columns); a thread owns one value column and every
-// LN-th state row of it (R rows in registers), so a token costs R multiply-adds for the state, R for the result
-// and log2(LN) shuffles.  Tokens are staged through shared memory TC at a time.  The state of a sequence lives in
+// LN-th group of four state rows of it (R rows in registers, read from shared memory 16 bytes at a time), so a token costs R multiply-adds for the state, R for the result
+// and log2(LN) shuffles.  Tokens are staged through shared memory a chunk at a time in two buffers: asynchronous
+// copies bring the next chunk's rows while the block works through the present one.  The state of a sequence lives in
 // its slot as [heads][vdim][state] float32, is read at the start of the entry and written at its end, so a
 // prompt may be cut anywhere and a decoded token is the same kernel with one token.
 #include "common.cuh"
+#include <cstdlib>
 
 namespace {
 constexpr int MAX_TAPS = 16;
 constexpr int R = 16;           // state rows a thread holds
-constexpr int TC = 16;          // tokens staged at a time
+constexpr int MAX_TC = 16;      // tokens staged at a time at most
 
 struct ConvArgs {
   const float* in; long long in_stride; int col0;       // u = in[row][col0 + c]
@@ -74,18 +76,16 @@ struct SsmArgs {
   float* state;                                                        // [slots][heads][vdim][n_state]
   const int* entry_q_start; const int* entry_q_len; const int* entry_slot;
   float* out; long long out_stride;                                    // [row][heads * vdim]
-  int heads, groups, vdim, n_state, ln, cols_per_block;
+  int heads, groups, vdim, n_state, cols_per_block, tc, vec;   // vec: every staged row starts 16-byte aligned
 };
 
-__global__ void __launch_bounds__(1024)
+template <int LN>
+__global__ void __launch_bounds__(512)
 ssm_scan_kernel(SsmArgs p) {
-  extern __shared__ float sm[];
-  const int LN = p.ln, NP = R * LN, PB = p.cols_per_block;
-  float* Bs = sm;                       // [TC][NP]
-  float* Cs = Bs + TC * NP;             // [TC][NP]
-  float* xs = Cs + TC * NP;             // [TC][PB]
-  float* dts = xs + TC * PB;            // [TC]
-  float* decs = dts + TC;               // [TC]
+  extern __shared__ __align__(16) float sm[];
+  constexpr int NP = R * LN;
+  const int PB = p.cols_per_block, TC = p.tc;
+  const int BUF = (TC * (2 * NP + PB + 2) + 3) & ~3;   // per buffer (16-byte aligned): B, C [TC][NP], x [TC][PB], dt and the decay [TC]
   pdl_enter();
   const int h = blockIdx.x, e = blockIdx.y, p0 = blockIdx.z * PB;
   const int tid = threadIdx.x;
@@ -96,53 +96,115 @@ ssm_scan_kernel(SsmArgs p) {
   const int r0 = p.entry_q_start[e], len = p.entry_q_len[e];
   const float bias = p.dt_bias[h], neg_a = -expf(p.a_log[h]), dskip = p.d_skip[h];
   float* st = p.state + (((size_t)p.entry_slot[e] * p.heads + h) * p.vdim + (valid ? col : 0)) * p.n_state;
-  float S[R];
+  float S[R];                              // S[4 j + c] is state row 4 (j LN + ln) + c: a 16-byte load per four rows
 #pragma unroll
   for (int i = 0; i < R; ++i) {
-    const int n = i * LN + ln;
+    const int n = 4 * ((i >> 2) * LN + ln) + (i & 3);
     S[i] = (valid && n < p.n_state) ? st[n] : 0.0f;
   }
-  for (int t0 = 0; t0 < len; t0 += TC) {
+  // the rows of the tokens from t0 on, asked for (asynchronous copies); rows past the state's size are zeros
+  auto stage = [&](int t0, float* buf) {
     const int nt = min(TC, len - t0);
-    __syncthreads();
-    for (int idx = tid; idx < nt * NP; idx += blockDim.x) {
-      const int tt = idx / NP, n = idx - tt * NP;
-      const float* row = p.xbc + (size_t)(r0 + t0 + tt) * p.xbc_stride;
-      const bool on = n < p.n_state;
-      Bs[idx] = on ? row[p.b_col + g * p.n_state + n] : 0.0f;
-      Cs[idx] = on ? row[p.c_col + g * p.n_state + n] : 0.0f;
+    float* Bs = buf; float* Cs = Bs + TC * NP; float* xs = Cs + TC * NP; float* dts = xs + TC * PB;
+    if (p.vec) {
+      for (int idx = tid; idx < nt * (NP / 4); idx += blockDim.x) {
+        const int tt = idx / (NP / 4), n = 4 * (idx - tt * (NP / 4));
+        const float* row = p.xbc + (size_t)(r0 + t0 + tt) * p.xbc_stride + g * p.n_state + n;
+        if (n < p.n_state) {
+          cp_async_f32x4(Bs + tt * NP + n, row + p.b_col);
+          cp_async_f32x4(Cs + tt * NP + n, row + p.c_col);
+        } else {
+          *reinterpret_cast<float4*>(Bs + tt * NP + n) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+          *reinterpret_cast<float4*>(Cs + tt * NP + n) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+      }
+      const int pq = PB >> 2;
+      for (int idx = tid; idx < nt * pq; idx += blockDim.x) {
+        const int tt = idx / pq, c = 4 * (idx - tt * pq);
+        if (p0 + c < p.vdim) cp_async_f32x4(xs + tt * PB + c, p.xbc + (size_t)(r0 + t0 + tt) * p.xbc_stride + p.x_col + h * p.vdim + p0 + c);
+        else *reinterpret_cast<float4*>(xs + tt * PB + c) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      }
+    } else {
+      for (int idx = tid; idx < nt * NP; idx += blockDim.x) {
+        const int tt = idx / NP, n = idx - tt * NP;
+        const float* row = p.xbc + (size_t)(r0 + t0 + tt) * p.xbc_stride + g * p.n_state + n;
+        if (n < p.n_state) {
+          cp_async_f32(Bs + idx, row + p.b_col);
+          cp_async_f32(Cs + idx, row + p.c_col);
+        } else {
+          Bs[idx] = Cs[idx] = 0.0f;
+        }
+      }
+      for (int idx = tid; idx < nt * PB; idx += blockDim.x) {
+        const int tt = idx / PB, c = idx - tt * PB;
+        if (p0 + c < p.vdim) cp_async_f32(xs + idx, p.xbc + (size_t)(r0 + t0 + tt) * p.xbc_stride + p.x_col + h * p.vdim + p0 + c);
+        else xs[idx] = 0.0f;
+      }
     }
-    for (int idx = tid; idx < nt * PB; idx += blockDim.x) {
-      const int tt = idx / PB, c = idx - tt * PB;
-      xs[idx] = p0 + c < p.vdim ? p.xbc[(size_t)(r0 + t0 + tt) * p.xbc_stride + p.x_col + h * p.vdim + p0 + c] : 0.0f;
-    }
-    if (tid < nt) {
-      const float raw = p.dt[(size_t)(r0 + t0 + tid) * p.dt_stride + h] + bias;
+    for (int tt = tid; tt < nt; tt += blockDim.x) cp_async_f32(dts + tt, p.dt + (size_t)(r0 + t0 + tt) * p.dt_stride + h);
+    cp_async_commit();
+  };
+  // once the copies are in: the step size and the decay of every staged token
+  auto prepare = [&](int nt, float* buf) {
+    float* dts = buf + TC * (2 * NP + PB); float* decs = dts + TC;
+    for (int tt = tid; tt < nt; tt += blockDim.x) {
+      const float raw = dts[tt] + bias;
       const float dtv = raw > 20.0f ? raw : log1pf(expf(raw));
-      dts[tid] = dtv;
-      decs[tid] = expf(neg_a * dtv);
+      dts[tt] = dtv;
+      decs[tt] = expf(neg_a * dtv);
     }
+  };
+  if (len > 0) {
+    stage(0, sm);
+    cp_async_wait_all();
     __syncthreads();
+    prepare(min(TC, len), sm);
+    __syncthreads();
+  }
+  int which = 0;
+  for (int t0 = 0; t0 < len; t0 += TC, which ^= 1) {
+    const int nt = min(TC, len - t0);
+    const bool more = t0 + TC < len;
+    float* cur = sm + which * BUF;
+    float* nxt = sm + (which ^ 1) * BUF;          // last read two chunks ago, before the barriers of the last turn
+    if (more) stage(t0 + TC, nxt);
+    const float* Bs = cur; const float* Cs = Bs + TC * NP; const float* xs = Cs + TC * NP; const float* dts = xs + TC * PB;
+    const float* decs = dts + TC;
+#pragma unroll 2
     for (int tt = 0; tt < nt; ++tt) {
       const float dtv = dts[tt], dec = decs[tt];
       const float xv = pl < PB ? xs[tt * PB + pl] : 0.0f;
       const float bx = dtv * xv;
-      const float* b = Bs + tt * NP + ln;
-      const float* c = Cs + tt * NP + ln;
-      float y = 0.0f;
+      const float4* b4 = reinterpret_cast<const float4*>(Bs + tt * NP) + ln;
+      const float4* c4 = reinterpret_cast<const float4*>(Cs + tt * NP) + ln;
+      float y0 = 0.0f, y1 = 0.0f, y2 = 0.0f, y3 = 0.0f;      // four chains: no addition waits on the one before it
 #pragma unroll
-      for (int i = 0; i < R; ++i) {
-        S[i] = fmaf(dec, S[i], bx * b[i * LN]);
-        y = fmaf(S[i], c[i * LN], y);
+      for (int j = 0; j < R / 4; ++j) {
+        const float4 b = b4[j * LN], c = c4[j * LN];
+        S[4 * j] = fmaf(dec, S[4 * j], bx * b.x);
+        S[4 * j + 1] = fmaf(dec, S[4 * j + 1], bx * b.y);
+        S[4 * j + 2] = fmaf(dec, S[4 * j + 2], bx * b.z);
+        S[4 * j + 3] = fmaf(dec, S[4 * j + 3], bx * b.w);
+        y0 = fmaf(S[4 * j], c.x, y0);
+        y1 = fmaf(S[4 * j + 1], c.y, y1);
+        y2 = fmaf(S[4 * j + 2], c.z, y2);
+        y3 = fmaf(S[4 * j + 3], c.w, y3);
       }
-      for (int o = LN >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-      if (valid && ln == 0) p.out[(size_t)(r0 + t0 + tt) * p.out_stride + h * p.vdim + col] = fmaf(dskip, xv, y);
+      float yo = (y0 + y1) + (y2 + y3);
+      for (int o = LN >> 1; o > 0; o >>= 1) yo += __shfl_xor_sync(0xffffffffu, yo, o);
+      if (valid && ln == 0) p.out[(size_t)(r0 + t0 + tt) * p.out_stride + h * p.vdim + col] = fmaf(dskip, xv, yo);
+    }
+    if (more) {
+      cp_async_wait_all();
+      __syncthreads();
+      prepare(min(TC, len - t0 - TC), nxt);
+      __syncthreads();
     }
   }
   if (valid) {
 #pragma unroll
     for (int i = 0; i < R; ++i) {
-      const int n = i * LN + ln;
+      const int n = 4 * ((i >> 2) * LN + ln) + (i & 3);
       if (n < p.n_state) st[n] = S[i];
     }
   }
@@ -169,25 +231,36 @@ IFX_API int ifx_ssm_scan(const float* xbc, long long xbc_stride, int x_col, int 
                          long long dt_stride, const float* dt_bias, const float* a_log, const float* d_skip, float* state,
                          const int* entry_q_start, const int* entry_q_len, const int* entry_slot, int n_entries,
                          float* out, long long out_stride, int heads, int groups, int vdim, int n_state,
-                         cudaStream_t stream) {
+                         int n_rows, cudaStream_t stream) {
   if (n_entries <= 0) return 0;
   if (heads < 1 || groups < 1 || heads % groups || vdim < 1 || n_state < 1 || n_state > R * 32 || heads > 65535 * 32)
     return IFX_ERR_UNSUPPORTED;
   int ln = 1;
   while (R * ln < n_state) ln <<= 1;
-  int pb = 1024 / ln;
+  int pb = 512 / ln;
   if (pb > vdim) pb = vdim;
   // blocks of at most 256 threads where the columns allow it: more blocks to spread over the SMs
   while (pb * ln > 256 && pb % 2 == 0 && pb > 8) pb >>= 1;
+  if (const char* force = getenv("IFX_TRY_PB_SSM")) pb = atoi(force) < pb ? atoi(force) : pb;
   const int threads = (pb * ln + 31) / 32 * 32;
+  int tc = n_rows <= n_entries ? 1 : MAX_TC;      // single tokens stage one
+  while (tc > 1 && (size_t)2 * (tc * (2 * R * ln + pb + 2) + 3) * sizeof(float) > 96 * 1024) tc >>= 1;
+  const int vec = !((n_state | vdim | pb | x_col | b_col | c_col) & 3) && !(xbc_stride & 3) && !((uintptr_t)xbc & 15);
   SsmArgs p{xbc, xbc_stride, x_col, b_col, c_col, dt, dt_stride, dt_bias, a_log, d_skip, state, entry_q_start, entry_q_len,
-            entry_slot, out, out_stride, heads, groups, vdim, n_state, ln, pb};
-  const size_t smem = ((size_t)TC * (2 * R * ln + pb) + 2 * TC) * sizeof(float);
-  if (smem > 48 * 1024) {
-    cudaError_t err = cudaFuncSetAttribute(ssm_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (err != cudaSuccess) return (int)err;
-  }
-  const int rc = launch_pdl(ssm_scan_kernel, dim3(heads, n_entries, (vdim + pb - 1) / pb), dim3(threads), smem, stream, p);
+            entry_slot, out, out_stride, heads, groups, vdim, n_state, pb, tc, vec};
+  const size_t smem = (size_t)2 * (tc * (2 * R * ln + pb + 2) + 3) * sizeof(float);
+  const dim3 grid(heads, n_entries, (vdim + pb - 1) / pb), block(threads);
+  int rc = IFX_ERR_UNSUPPORTED;
+#define IFX_SSM_CASE(L)                                                                                             \
+  case L: {                                                                                                         \
+    if (smem > 48 * 1024) {                                                                                         \
+      cudaError_t err = cudaFuncSetAttribute(ssm_scan_kernel<L>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      if (err != cudaSuccess) return (int)err;                                                                      \
+    }                                                                                                               \
+    rc = launch_pdl(ssm_scan_kernel<L>, grid, block, smem, stream, p);                                              \
+  } break;
+  switch (ln) { IFX_SSM_CASE(1) IFX_SSM_CASE(2) IFX_SSM_CASE(4) IFX_SSM_CASE(8) IFX_SSM_CASE(16) IFX_SSM_CASE(32) }
+#undef IFX_SSM_CASE
   return rc ? rc : IFX_LAUNCH_CHECK();
 }
 

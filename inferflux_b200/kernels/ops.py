@@ -173,12 +173,13 @@ def _lib():
         lib.ifx_causal_conv.argtypes = [c_void_p, c_ll, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                         c_void_p, c_int, c_int, c_void_p, c_ll, c_int, c_int, c_void_p]
         lib.ifx_ssm_scan.argtypes = [c_void_p, c_ll, c_int, c_int, c_int, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_void_p,
-                                     c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_void_p]
+                                     c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_int,
+                                     c_void_p]
         lib.ifx_gated_group_norm.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_int, c_ll, c_int, c_int, c_int,
                                              c_float, c_void_p]
         lib.ifx_delta_rule_scan.argtypes = [c_void_p, c_ll, c_int, c_int, c_int, c_int, c_void_p, c_ll, c_void_p, c_void_p,
                                             c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_ll, c_int, c_int, c_int,
-                                            c_float, c_float, c_void_p]
+                                            c_float, c_float, c_int, c_void_p]
         lib.ifx_head_norm_gate.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_int, c_ll, c_int, c_int, c_int,
                                            c_float, c_int, c_void_p]
         lib.ifx_qkv_norm_rope_write.argtypes = [c_void_p, c_int, c_ll, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
@@ -1522,7 +1523,7 @@ def ssm_scan(xbc: torch.Tensor, x_col: int, b_col: int, c_col: int, dt: torch.Te
     _check(_lib().ifx_ssm_scan(_ptr(xbc), xbc.stride(0), x_col, b_col, c_col, _ptr(dt), dt.stride(0), _ptr(dt_bias),
                                _ptr(a_log), _ptr(d_skip), _ptr(state), _ptr(entry_q_start), _ptr(entry_q_len),
                                _ptr(entry_slot), n_entries, _ptr(out), out.stride(0), heads, groups, vdim, n_state,
-                               _stream()), "ssm_scan")
+                               n, _stream()), "ssm_scan")
     return out
 
 
@@ -1559,7 +1560,7 @@ def delta_rule_scan(proj: torch.Tensor, r_col: int, k_col: int, v_col: int, a_co
     _check(_lib().ifx_delta_rule_scan(_ptr(proj), proj.stride(0), r_col, k_col, v_col, a_col, _ptr(w_raw), w_raw.stride(0),
                                       _ptr(w0), _ptr(a_bias), _ptr(state), _ptr(entry_q_start), _ptr(entry_q_len),
                                       _ptr(entry_slot), n_entries, _ptr(out), out.stride(0), heads, dim, vdim,
-                                      float(decay_scale), float(key_eps), _stream()), "delta_rule_scan")
+                                      float(decay_scale), float(key_eps), n, _stream()), "delta_rule_scan")
     return out
 
 

@@ -15,7 +15,6 @@
 // its slot as [heads][vdim][state] float32, is read at the start of the entry and written at its end, so a
 // prompt may be cut anywhere and a decoded token is the same kernel with one token.
 #include "common.cuh"
-#include <cstdlib>
 
 namespace {
 constexpr int MAX_TAPS = 16;
@@ -241,7 +240,6 @@ IFX_API int ifx_ssm_scan(const float* xbc, long long xbc_stride, int x_col, int 
   if (pb > vdim) pb = vdim;
   // blocks of at most 256 threads where the columns allow it: more blocks to spread over the SMs
   while (pb * ln > 256 && pb % 2 == 0 && pb > 8) pb >>= 1;
-  if (const char* force = getenv("IFX_TRY_PB_SSM")) pb = atoi(force) < pb ? atoi(force) : pb;
   const int threads = (pb * ln + 31) / 32 * 32;
   int tc = n_rows <= n_entries ? 1 : MAX_TC;      // single tokens stage one
   while (tc > 1 && (size_t)2 * (tc * (2 * R * ln + pb + 2) + 3) * sizeof(float) > 96 * 1024) tc >>= 1;

@@ -179,7 +179,7 @@ def _lib():
                                              c_float, c_void_p]
         lib.ifx_delta_rule_scan.argtypes = [c_void_p, c_ll, c_int, c_int, c_int, c_int, c_void_p, c_ll, c_void_p, c_void_p,
                                             c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_ll, c_int, c_int, c_int,
-                                            c_float, c_float, c_int, c_void_p]
+                                            c_float, c_float, c_int, c_void_p, c_void_p]
         lib.ifx_head_norm_gate.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_int, c_ll, c_int, c_int, c_int,
                                            c_float, c_int, c_void_p]
         lib.ifx_qkv_norm_rope_write.argtypes = [c_void_p, c_int, c_ll, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
@@ -1557,10 +1557,16 @@ def delta_rule_scan(proj: torch.Tensor, r_col: int, k_col: int, v_col: int, a_co
     _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, vdim, dim),
           "delta_rule_scan: state float32 [slots, heads, vdim, dim]")
     _need(out.dtype == torch.float32 and out.stride(1) == 1 and tuple(out.shape) == (n, heads * vdim), "delta_rule_scan: out")
+    # a step with portions: the unit key, decay and removal rate of all its rows by a kernel ahead of the scan
+    prep = torch.empty((n, 3 * heads * dim), dtype=torch.float32, device=proj.device) if n > n_entries else None
     _check(_lib().ifx_delta_rule_scan(_ptr(proj), proj.stride(0), r_col, k_col, v_col, a_col, _ptr(w_raw), w_raw.stride(0),
                                       _ptr(w0), _ptr(a_bias), _ptr(state), _ptr(entry_q_start), _ptr(entry_q_len),
                                       _ptr(entry_slot), n_entries, _ptr(out), out.stride(0), heads, dim, vdim,
-                                      float(decay_scale), float(key_eps), n, _stream()), "delta_rule_scan")
+                                      float(decay_scale), float(key_eps), n, _ptr(prep) if prep is not None else None,
+                                      _stream()), "delta_rule_scan")
+    if prep is not None:
+        global launch_count
+        launch_count += 1
     return out
 
 

@@ -514,14 +514,55 @@ __global__ void activation_kernel(const float* __restrict__ z, long long z_strid
   }
 }
 
+// Four neighbouring columns a thread with 16-byte loads, where rows, strides and addresses allow it.
+template <typename T>
+__global__ void activation_vec_kernel(const float* __restrict__ z, long long z_stride, int parts, long long part_stride,
+                                      T* __restrict__ out, long long out_stride, int quads, long long total, int act) {
+  pdl_enter();
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (; idx < total; idx += stride) {
+    const long long m = idx / quads;
+    const int c = 4 * (int)(idx - m * quads);
+    float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int s = 0; s < parts; ++s) {
+      const float4 a = *reinterpret_cast<const float4*>(z + (size_t)s * part_stride + m * z_stride + c);
+      v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+    }
+    v.x = apply_activation(v.x, act); v.y = apply_activation(v.y, act);
+    v.z = apply_activation(v.z, act); v.w = apply_activation(v.w, act);
+    T* o = out + m * out_stride + c;
+    if constexpr (sizeof(T) == 2) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+      uint2 packed;
+      packed.x = *reinterpret_cast<unsigned*>(&lo);
+      packed.y = *reinterpret_cast<unsigned*>(&hi);
+      *reinterpret_cast<uint2*>(o) = packed;
+    } else {
+      *reinterpret_cast<float4*>(o) = v;
+    }
+  }
+}
+
 IFX_API int ifx_activation(const float* z, long long z_stride, int parts, long long part_stride, void* out, int out_dtype,
                            long long out_stride, int m, int cols, int act, cudaStream_t stream) {
   const long long total = (long long)m * cols;
   if (total <= 0) return 0;
   if (act < 0 || act > 4) return IFX_ERR_UNSUPPORTED;
+  int rc;
+  if (!(cols & 3) && !((z_stride | part_stride | out_stride) & 3) && !((uintptr_t)z & 15) && !((uintptr_t)out & 15) &&
+      (out_dtype == IFX_F32 || out_dtype == IFX_BF16)) {
+    const long long quads = total / 4;
+    long long vblocks = (quads + 255) / 256;
+    if (vblocks > 148 * 16) vblocks = 148 * 16;
+    if (out_dtype == IFX_F32)
+      rc = launch_pdl(activation_vec_kernel<float>, dim3((int)vblocks), dim3(256), 0, stream, z, z_stride, parts, part_stride, (float*)out, out_stride, cols / 4, quads, act);
+    else
+      rc = launch_pdl(activation_vec_kernel<bf16>, dim3((int)vblocks), dim3(256), 0, stream, z, z_stride, parts, part_stride, (bf16*)out, out_stride, cols / 4, quads, act);
+    return rc ? rc : IFX_LAUNCH_CHECK();
+  }
   long long blocks = (total + 255) / 256;
   if (blocks > 148 * 32) blocks = 148 * 32;
-  int rc;
   if (out_dtype == IFX_F32)
     rc = launch_pdl(activation_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, z, z_stride, parts, part_stride, (float*)out, out_stride, cols, total, act);
   else if (out_dtype == IFX_BF16)

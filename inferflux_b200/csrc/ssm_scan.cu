@@ -264,25 +264,41 @@ IFX_API int ifx_ssm_scan(const float* xbc, long long xbc_stride, int x_col, int 
 
 namespace {
 // out[t][g] = N(y[t][g] * silu(z[t][g])) * w[g] over each of `groups` equal parts of a row, N(v) = v / sqrt(mean(v^2) + eps).
-// A block a (row, group); the gate comes ahead of the norm.
+// A block a (row, group); the gate comes ahead of the norm.  A thread keeps its first eight gated values between
+// the sum of squares and the result, so that their loads are asked for together and nothing is computed twice.
 template <typename TO>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 gated_group_norm_kernel(const float* __restrict__ y, long long y_stride, const float* __restrict__ z, long long z_stride,
                         const float* __restrict__ w, TO* __restrict__ out, long long out_stride, int group_width, float eps) {
   __shared__ float scratch[32];
+  constexpr int KEEP = 8;
   pdl_enter();
   const int t = blockIdx.x, c0 = blockIdx.y * group_width;
   const float* yr = y + (size_t)t * y_stride + c0;
   const float* zr = z + (size_t)t * z_stride + c0;
+  float keep[KEEP];
   float ss = 0.0f;
-  for (int i = threadIdx.x; i < group_width; i += blockDim.x) {
+#pragma unroll
+  for (int j = 0; j < KEEP; ++j) {
+    const int i = threadIdx.x + j * blockDim.x;
+    const float g = i < group_width ? zr[i] : 0.0f;
+    const float v = i < group_width ? yr[i] * (g / (1.0f + expf(-g))) : 0.0f;
+    keep[j] = v;
+    ss = fmaf(v, v, ss);
+  }
+  for (int i = threadIdx.x + KEEP * blockDim.x; i < group_width; i += blockDim.x) {
     const float g = zr[i];
     const float v = yr[i] * (g / (1.0f + expf(-g)));
     ss = fmaf(v, v, ss);
   }
   const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)group_width + eps);
   TO* o = out + (size_t)t * out_stride + c0;
-  for (int i = threadIdx.x; i < group_width; i += blockDim.x) {
+#pragma unroll
+  for (int j = 0; j < KEEP; ++j) {
+    const int i = threadIdx.x + j * blockDim.x;
+    if (i < group_width) o[i] = Num<TO>::from_f(keep[j] * inv * w[c0 + i]);
+  }
+  for (int i = threadIdx.x + KEEP * blockDim.x; i < group_width; i += blockDim.x) {
     const float g = zr[i];
     const float v = yr[i] * (g / (1.0f + expf(-g)));
     o[i] = Num<TO>::from_f(v * inv * w[c0 + i]);
@@ -297,7 +313,7 @@ IFX_API int ifx_gated_group_norm(const float* y, long long y_stride, const float
                                  float eps, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (groups < 1 || groups > 65535 || group_width < 1) return IFX_ERR_UNSUPPORTED;
-  const int threads = group_width >= 256 ? 256 : (group_width + 31) / 32 * 32;
+  const int threads = group_width >= 4096 ? 1024 : group_width >= 1024 ? 512 : group_width >= 256 ? 256 : (group_width + 31) / 32 * 32;
   int rc;
   if (out_dtype == IFX_BF16)
     rc = launch_pdl(gated_group_norm_kernel<bf16>, dim3(n_rows, groups), dim3(threads), 0, stream, y, y_stride, z, z_stride, w,

@@ -211,7 +211,7 @@ def tekosun_config(size: str, layers: int):
     family's feed-forward width of which a token takes 4, and a shared expert of that width."""
     _, hidden, heads, kv_heads, inter, vocab, _ = SIZES[size]
     ff = inter // 4 // 8 * 8
-    moe = dict(kind="moe", expert=dict(ff=ff), router=dict(experts=16, top=4, scale=2.5), shared=dict(ff=ff))
+    moe = dict(kind="moe", expert=dict(ff=ff), router=dict(experts=16, top=4, scale=2.0), shared=dict(ff=ff))
     attn = dict(type="attention", mlp=moe, mixer=dict(
         heads=heads, kv_heads=kv_heads, dim=128, vdim=128, scale=128 ** -0.5, v_mix=True, mask=dict(size=1024),
         rot=dict(dims=128, base=500000.0, scaling=dict(factor=8.0, low=1.0, high=4.0, original=8192))))

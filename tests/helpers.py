@@ -295,7 +295,7 @@ TK_A = dict(architecture="Tekosun", width=64, vocab=300, norm=dict(eps=1e-5), em
     dict(type="mamba2", mixer=dict(heads=3, vdim=12, state=8, groups=1, conv=4, norm_groups=1), mlp=None),
     dict(type="general_delta", mixer=dict(heads=2, dim=12), mlp=_TK_MOE(32, 4, 1, 0.5)),
     dict(type="attention", mixer=dict(heads=2, kv_heads=2, dim=32, vdim=24, scale=0.4, v_mix=True, mask=dict(size=33),
-                                      rot=dict(dims=32, base=300.0)), mlp=_TK_MOE(40, 5, 2, 2.5, 56))])
+                                      rot=dict(dims=32, base=300.0)), mlp=_TK_MOE(40, 5, 2, 2.25, 56))])
 # B: sizes that are no multiple of 4 or 8 anywhere, two state-space groups and two norm groups, two taps, an attention
 # without window, rotation, value mixing or key/value head count, a window shorter than a page, every expert chosen,
 # no embedding scale, a decay projection of five

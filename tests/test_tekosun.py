@@ -189,8 +189,8 @@ def test_plain_carry_over_routing_and_bands():
     # no removal and no decay: plain linear attention
     o_lin, _ = plain.delta_scan(r, k, v, torch.ones_like(dec), torch.zeros_like(rate))
     assert torch.allclose(o_lin[6, 0], sum((r[6, 0] @ k[j, 0]) * v[j, 0] for j in range(7)))
-    ids, wts = plain.route(torch.tensor([[1.0, 3.0, 3.0, -1.0]], dtype=torch.float64), 2, 2.5)
-    assert ids.tolist() == [[1, 2]] and torch.allclose(wts, torch.tensor([[1.25, 1.25]], dtype=torch.float64))
+    ids, wts = plain.route(torch.tensor([[1.0, 3.0, 3.0, -1.0]], dtype=torch.float64), 2, 2.25)
+    assert ids.tolist() == [[1, 2]] and torch.allclose(wts, torch.tensor([[1.125, 1.125]], dtype=torch.float64))
     ids, wts = plain.route(torch.tensor([[0.0, math.log(3.0)]], dtype=torch.float64), 1, 1.0)
     assert ids.tolist() == [[1]] and torch.allclose(wts, torch.ones(1, 1, dtype=torch.float64))   # one choice: its score over itself
     see = plain.visible(3, 10, 4)
@@ -452,7 +452,7 @@ def test_attention_mixer_alone(dtype, name, layer, mode):
 @gpu
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("hidden,ff,experts,top,shared,scale,rows", [
-    (64, 40, 5, 2, 24, 1.7, 3), (64, 40, 5, 2, None, 2.5, 300), (50, 35, 3, 3, 9, 1.0, 70), (50, 18, 3, 1, None, 3.0, 5),
+    (64, 40, 5, 2, 24, 1.7, 3), (64, 40, 5, 2, None, 2.25, 300), (50, 35, 3, 3, 9, 1.0, 70), (50, 18, 3, 1, None, 3.0, 5),
     (128, 48, 12, 3, 64, 2.0, 1), (96, 200, 40, 8, 120, 0.5, 130),
     (128, 48, 12, 3, 64, 2.0, 400)])                                    # bfloat16, 1,200 pairs: the tcgen05 tiles
 def test_squared_relu_experts_alone(dtype, hidden, ff, experts, top, shared, scale, rows):

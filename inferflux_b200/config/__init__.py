@@ -1,11 +1,11 @@
-from .model_config import ConfigError, KunonexConfig, ModelConfig, PemoraxConfig, Qwen2Config, TekosunConfig, read_config_dict
+from .model_config import ConfigError, KunonexConfig, MalazenConfig, ModelConfig, PemoraxConfig, Qwen2Config, TekosunConfig, read_config_dict
 from .engine_config import EngineConfig
 from .spec import PartSpec, LayerSpec, Run, ModelSpec
 from .registry import (register_architecture, register_part, part_class, load_config,
                        build_spec, resolve_architecture, registered_architectures)
 
 __all__ = [
-    "ConfigError", "KunonexConfig", "ModelConfig", "PemoraxConfig", "Qwen2Config", "TekosunConfig", "read_config_dict", "EngineConfig",
+    "ConfigError", "KunonexConfig", "MalazenConfig", "ModelConfig", "PemoraxConfig", "Qwen2Config", "TekosunConfig", "read_config_dict", "EngineConfig",
     "PartSpec", "LayerSpec", "Run", "ModelSpec", "register_architecture", "register_part",
     "part_class", "load_config", "build_spec", "resolve_architecture",
     "registered_architectures",

@@ -660,3 +660,160 @@ class TekosunConfig(ModelConfig):
             layers.append({"type": l.type, "mixer": m, "mlp": mlp})
         return {"architecture": self.architecture, "width": self.width, "vocab": self.vocab, "norm": {"eps": self.norm_eps},
                 "embedding": {"scale": self.embedding_scale}, "layers": layers}
+
+
+@dataclass(frozen=True)
+class MalazenLayer:
+    """One layer of a Malazen model as config.json gives it: the mixer's sizes and constants (checked, defaults
+    filled in) and its feed-forward (``None`` = none; ``kind`` ``dense`` with ``ff`` and ``limit``)."""
+
+    type: str = ""
+    mixer: Dict[str, Any] = field(default_factory=dict)
+    mlp: Optional[Dict[str, Any]] = None
+
+
+@dataclass(frozen=True)
+class MalazenConfig(ModelConfig):
+    """``Malazen``: a decoder whose layers are listed one by one in config.json (``layers``: ``type``, the mixer's
+    sizes under ``mixer``, the feed-forward under ``mlp`` or null), pre-norm with an RMS norm taken over
+    ``norm.groups`` equal parts of the row.  The mixer ``parallel`` is a weighted sum of a pair of mixers on one
+    input: ``left`` grouped-query attention without rotation (biases, a query that grows with the logarithm of its
+    position, a score that loses a logarithm of the distance) and ``right`` gated linear attention (a decay per key
+    channel from a small projection, a normed and silu-gated output).  The mixer ``latent_attention`` keeps one
+    normed latent and one rotated key part per token (neighbouring pairs rotate, frequencies optionally stretched),
+    attends within a window and has a learned sink per head.  Feed-forwards are gated with clamped inputs.  A
+    stretch of layers (``loop``: ``start``, ``stop``, ``times``) may run several times in a row on the same
+    weights, the embedding's output being added to the stream ahead of every pass but the first.  The output head
+    is the embedding table."""
+
+    width: int = 0
+    vocab: int = 0
+    norm_eps: float = 1e-6
+    norm_groups: int = 1
+    layers: List[MalazenLayer] = field(default_factory=list)
+    loop_start: int = 0
+    loop_stop: int = 0
+    loop_times: int = 0              # 0 = the model has no loop
+
+    ARCHITECTURE = "Malazen"
+    MODEL_TYPE = "malazen"
+
+    @staticmethod
+    def _left(m: Dict[str, Any], where: str) -> Dict[str, Any]:
+        heads, dim = _require_int(m, "heads"), _require_int(m, "dim")
+        out = {"heads": heads, "kv_heads": _require_int(m, "kv_heads") if m.get("kv_heads") is not None else heads,
+               "dim": dim, "vdim": _require_int(m, "vdim") if m.get("vdim") is not None else dim,
+               "scale": _require_number(m, "scale", where) if m.get("scale") is not None else float(dim) ** -0.5,
+               "q_temp": None}
+        if heads % out["kv_heads"]:
+            raise ConfigError(f"{where}: heads {heads} is not a multiple of kv_heads {out['kv_heads']}")
+        qt = _sub(m, "q_temp", where, optional=True)
+        if qt is not None:
+            out["q_temp"] = {"coef": _require_number(qt, "coef", where + " q_temp"), "every": _require_int(qt, "every")}
+        return out
+
+    @staticmethod
+    def _right(m: Dict[str, Any], where: str) -> Dict[str, Any]:
+        heads, dim = _require_int(m, "heads"), _require_int(m, "dim")
+        tau = _require_number(m, "tau", where)
+        if tau <= 0:
+            raise ConfigError(f"{where}: tau must be positive")
+        return {"heads": heads, "dim": dim, "vdim": _require_int(m, "vdim") if m.get("vdim") is not None else dim, "tau": tau}
+
+    @staticmethod
+    def _latent(m: Dict[str, Any], where: str) -> Dict[str, Any]:
+        dim, rot_dim = _require_int(m, "dim", 0), _require_int(m, "rot_dim", 0) if m.get("rot_dim") is not None else 0
+        if dim + rot_dim < 1:
+            raise ConfigError(f"{where}: dim + rot_dim must be positive")
+        out = {"heads": _require_int(m, "heads"), "dim": dim, "rot_dim": rot_dim, "vdim": _require_int(m, "vdim"),
+               "kv_rank": _require_int(m, "kv_rank"),
+               "scale": _require_number(m, "scale", where) if m.get("scale") is not None else float(dim + rot_dim) ** -0.5,
+               "window": 0, "rot": None}
+        mask = _sub(m, "mask", where, optional=True)
+        if mask is not None:
+            out["window"] = _require_int(mask, "size")
+        if rot_dim:
+            out["rot"] = PemoraxConfig._rot(m, where, rot_dim)
+            if out["rot"]["dims"] != rot_dim:
+                raise ConfigError(f"{where}: rot.dims {out['rot']['dims']} must equal rot_dim {rot_dim}")
+        return out
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "MalazenConfig":
+        width, vocab = _require_int(d, "width"), _require_int(d, "vocab")
+        norm = _sub(d, "norm", "config.json")
+        eps = _require_number(norm, "eps", "config.json norm")
+        groups = _require_int(norm, "groups") if norm.get("groups") is not None else 1
+        if eps <= 0:
+            raise ConfigError(f"norm eps must be positive, got {eps}")
+        if width % groups:
+            raise ConfigError(f"norm.groups {groups} does not divide the width {width}")
+        raw = d.get("layers")
+        if not isinstance(raw, list) or not raw:
+            raise ConfigError("config.json: 'layers' must be a non-empty list")
+        layers = []
+        for i, entry in enumerate(raw):
+            where = f"config.json layers[{i}]"
+            if not isinstance(entry, dict):
+                raise ConfigError(f"{where}: must be an object")
+            kind = entry.get("type")
+            mixer = _sub(entry, "mixer", where)
+            if kind == "parallel":
+                sizes = {"left": cls._left(_sub(mixer, "left", where + " mixer"), where + " mixer.left"),
+                         "right": cls._right(_sub(mixer, "right", where + " mixer"), where + " mixer.right"),
+                         "left_scale": _opt_number(mixer, "left_scale", 1.0), "right_scale": _opt_number(mixer, "right_scale", 1.0)}
+            elif kind == "latent_attention":
+                sizes = cls._latent(mixer, where + " mixer")
+            else:
+                raise ConfigError(f"{where}: type {kind!r} is not one of ['latent_attention', 'parallel']")
+            mlp = _sub(entry, "mlp", where, optional=True)
+            ff = None
+            if mlp is not None:
+                if mlp.get("kind") != "dense":
+                    raise ConfigError(f"{where}: mlp kind {mlp.get('kind')!r} is not one of ['dense']")
+                ff = {"kind": "dense", "ff": _require_int(mlp, "ff"), "limit": _require_number(mlp, "limit", where + " mlp")}
+                if ff["limit"] <= 0:
+                    raise ConfigError(f"{where}: mlp limit must be positive")
+            layers.append(MalazenLayer(type=kind, mixer=sizes, mlp=ff))
+        start = stop = times = 0
+        loop = d.get("loop")
+        if loop is not None:
+            if not isinstance(loop, dict):
+                raise ConfigError("config.json: 'loop' must be an object or null")
+            start, stop = _require_int(loop, "start", 0), _require_int(loop, "stop", 0)
+            times = _require_int(loop, "times", 1)
+            if not 0 <= start < stop <= len(layers):
+                raise ConfigError(f"config.json: loop {start}..{stop} does not lie within the {len(layers)} layers")
+        arch = d.get("architecture") or (d.get("architectures") or [cls.ARCHITECTURE])[0]
+        return cls(architectures=[str(arch)], model_type=str(d.get("model_type", "") or cls.MODEL_TYPE), width=width,
+                   vocab=vocab, norm_eps=eps, norm_groups=groups, layers=layers, loop_start=start, loop_stop=stop,
+                   loop_times=times)
+
+    @property
+    def vocab_size(self) -> int:
+        return self.vocab
+
+    @property
+    def eos_token_id(self) -> Optional[int]:
+        return None
+
+    def to_dict(self) -> Dict[str, Any]:
+        """The config.json this configuration was read from (its own keys)."""
+        layers = []
+        for l in self.layers:
+            m = {k: (dict(v) if isinstance(v, dict) else v) for k, v in l.mixer.items()}
+            if l.type == "parallel":
+                if m["left"]["q_temp"] is None:
+                    m["left"].pop("q_temp")
+            else:
+                window, rot = m.pop("window"), m.pop("rot")
+                if window:
+                    m["mask"] = {"size": window}
+                if rot:
+                    m["rot"] = {k: v for k, v in rot.items() if v is not None}
+            layers.append({"type": l.type, "mixer": m, "mlp": dict(l.mlp) if l.mlp else None})
+        out = {"architecture": self.architecture, "width": self.width, "vocab": self.vocab,
+               "norm": {"eps": self.norm_eps, "groups": self.norm_groups}, "layers": layers}
+        if self.loop_times:
+            out["loop"] = {"start": self.loop_start, "stop": self.loop_stop, "times": self.loop_times}
+        return out

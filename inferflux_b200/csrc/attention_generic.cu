@@ -44,7 +44,23 @@ struct AttnOptions {
   int sink;                   // 1 = the denominator has one more term exp(0)
   const float* gate;          // [N][gate_stride] float32 or null: out *= sigmoid(gate[row][head * v_dim + d])
   int gate_parts; long long gate_part_stride; int gate_stride;
+  float q_temp_coef;          // the query at position p counts 1 + coef * ln(floor((p + 1) / every) + 1) times; every = 0: none
+  int q_temp_every;
+  const float* dist_r1;       // [n_heads] or null: the score of key j loses r1[head] * ln(1 + r2[head] * (p - j))
+  const float* dist_r2;
+  const float* sink_value;    // [n_heads] or null: with a sink, its score (0 where null)
 };
+
+// What the options make of a raw product q . k: the query's temperature, the scale, the cap, the distance's toll.
+__device__ __forceinline__ float query_temperature(const AttnOptions& opt, int p) {
+  return opt.q_temp_every > 0 ? 1.0f + opt.q_temp_coef * logf((float)((p + 1) / opt.q_temp_every + 1)) : 1.0f;
+}
+__device__ __forceinline__ float shaped_score(const AttnOptions& opt, float dot, float scale_temp, float r1, float r2, int dist) {
+  float sc = dot * scale_temp;
+  if (opt.softcap > 0.0f) sc = opt.softcap * tanhf(sc / opt.softcap);
+  if (opt.dist_r1) sc -= r1 * log1pf(r2 * (float)dist);
+  return sc;
+}
 
 template <typename T, int NACC>
 __global__ void __launch_bounds__(256)
@@ -77,7 +93,9 @@ attn_paged_generic_kernel(const T* __restrict__ q, long long q_stride, T* __rest
 
   const int r0 = warp * 2, r1 = r0 + 1;
   // a sink is a key of score 0 without a value: the running maximum starts at 0 and the sum at exp(0)
-  float m[2] = {opt.sink ? 0.0f : -INFINITY, opt.sink ? 0.0f : -INFINITY}, l[2] = {opt.sink ? 1.0f : 0.0f, opt.sink ? 1.0f : 0.0f};
+  const float sink0 = opt.sink ? (opt.sink_value ? opt.sink_value[head] : 0.0f) : -INFINITY;
+  const float toll1 = opt.dist_r1 ? opt.dist_r1[head] : 0.0f, toll2 = opt.dist_r1 ? opt.dist_r2[head] : 0.0f;
+  float m[2] = {sink0, sink0}, l[2] = {opt.sink ? 1.0f : 0.0f, opt.sink ? 1.0f : 0.0f};
   float o[2][NACC];
 #pragma unroll
   for (int a = 0; a < NACC; ++a) { o[0][a] = 0.0f; o[1][a] = 0.0f; }
@@ -131,8 +149,7 @@ attn_paged_generic_kernel(const T* __restrict__ q, long long q_stride, T* __rest
         if (rr == 1 && !two) break;
         const int p = pos0 + r0 + rr;
         const bool visible = key <= p && (window <= 0 || key > p - window || key < opt.keep_first);
-        float sc = (rr ? s1 : s0) * scale;
-        if (opt.softcap > 0.0f) sc = opt.softcap * tanhf(sc / opt.softcap);
+        const float sc = shaped_score(opt, rr ? s1 : s0, scale * query_temperature(opt, p), toll1, toll2, visible ? p - key : 0);
         const float s = visible ? sc : -INFINITY;
         const float m_new = fmaxf(m[rr], warp_max(s));
         if (m_new == -INFINITY) continue;          // nothing visible to this row yet (warp-uniform)
@@ -207,6 +224,8 @@ attn_single_token_kernel(const T* __restrict__ q, long long q_stride, T* __restr
   if (window > 0) kstart = max(0, p - window + 1) & ~(BKEYS - 1);
   const int keep_end = window > 0 ? min((opt.keep_first + BKEYS - 1) & ~(BKEYS - 1), kstart) : 0;
   const int n_keep = keep_end / BKEYS, n_tiles = n_keep + (p - kstart) / BKEYS + 1;
+  const float scale_temp = scale * query_temperature(opt, p);
+  const float r1 = opt.dist_r1 ? opt.dist_r1[head] : 0.0f, r2 = opt.dist_r1 ? opt.dist_r2[head] : 0.0f;
   float m = -INFINITY, l = 0.0f, o[NACC];
 #pragma unroll
   for (int a = 0; a < NACC; ++a) o[a] = 0.0f;
@@ -240,8 +259,7 @@ attn_single_token_kernel(const T* __restrict__ q, long long q_stride, T* __restr
       } else {
         for (int d = 0; d < head_dim; ++d) dot = fmaf(qs[d], Num<T>::to_f(kr[d]), dot);
       }
-      sc = dot * scale;
-      if (opt.softcap > 0.0f) sc = opt.softcap * tanhf(sc / opt.softcap);
+      sc = shaped_score(opt, dot, scale_temp, r1, r2, p - key);
     }
     const float m_new = fmaxf(m, warp_max(sc));
     if (m_new == -INFINITY) continue;                 // warp-uniform: nothing visible in this tile
@@ -304,10 +322,11 @@ attn_single_token_kernel(const T* __restrict__ q, long long q_stride, T* __restr
   }
 #undef IFX_DIM_OF
   __syncthreads();
-  if (warp == 0) {                                    // the merge: warps in index order, the sink as one more term exp(0)
-    float mm = opt.sink ? 0.0f : -INFINITY;
+  if (warp == 0) {                                    // the merge: warps in index order, the sink as one more term exp(its score)
+    const float sink0 = opt.sink ? (opt.sink_value ? opt.sink_value[head] : 0.0f) : -INFINITY;
+    float mm = sink0;
     for (int w = 0; w < DEC_WARPS; ++w) mm = fmaxf(mm, wm[w]);
-    float ll = opt.sink ? expf(0.0f - mm) : 0.0f;
+    float ll = opt.sink ? expf(sink0 - mm) : 0.0f;
     float f[DEC_WARPS];
     for (int w = 0; w < DEC_WARPS; ++w) {
       f[w] = wm[w] == -INFINITY ? 0.0f : expf(wm[w] - mm);
@@ -391,15 +410,19 @@ int dispatch_generic(const void* q, long long q_stride, void* out, long long out
 // Query tiles are 16 tokens of one entry: tile_entry / tile_q0 list them.
 // head_dim and v_dim: any positive size up to 256; n_heads must be a multiple of n_kv.  The options are
 // those of AttnOptions; gate: float32 slices [gate_parts][N][gate_stride] whose sum is the gate's argument.
-IFX_API int ifx_attn_paged_generic_ex(const void* q, long long q_stride, void* out, long long out_stride, int dtype,
-                                      void* k_layer, void* v_layer, long long page_stride, int page_size,
-                                      const int* block_tables, int bt_stride,
-                                      const int* tile_entry, const int* tile_q0, int n_tiles,
-                                      const int* entry_q_start, const int* entry_q_len, const int* entry_ctx_start,
-                                      int n_heads, int n_kv, int head_dim, float scale, int window,
-                                      int v_dim, float softcap, int keep_first, int sink,
-                                      const float* gate, int gate_parts, long long gate_part_stride, int gate_stride,
-                                      int single_tokens, cudaStream_t stream) {
+// q_temp_every > 0: the query at position p is multiplied by 1 + q_temp_coef * ln(floor((p + 1) / q_temp_every) + 1);
+// dist_r1, dist_r2 ([n_heads] float32 or null): the score of key j loses r1 * ln(1 + r2 * (p - j)), after the cap;
+// sink_value ([n_heads] float32 or null): the sink's score where it is not 0.
+IFX_API int ifx_attn_paged_generic_ex2(const void* q, long long q_stride, void* out, long long out_stride, int dtype,
+                                       void* k_layer, void* v_layer, long long page_stride, int page_size,
+                                       const int* block_tables, int bt_stride,
+                                       const int* tile_entry, const int* tile_q0, int n_tiles,
+                                       const int* entry_q_start, const int* entry_q_len, const int* entry_ctx_start,
+                                       int n_heads, int n_kv, int head_dim, float scale, int window,
+                                       int v_dim, float softcap, int keep_first, int sink,
+                                       const float* gate, int gate_parts, long long gate_part_stride, int gate_stride,
+                                       int single_tokens, float q_temp_coef, int q_temp_every, const float* dist_r1,
+                                       const float* dist_r2, const float* sink_value, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (head_dim < 1 || head_dim > 256 || v_dim < 1 || v_dim > 256 || n_kv < 1 || n_heads % n_kv) return IFX_ERR_UNSUPPORTED;
   if (page_size <= 0 || (page_size & (page_size - 1))) return IFX_ERR_UNSUPPORTED;
@@ -409,7 +432,9 @@ IFX_API int ifx_attn_paged_generic_ex(const void* q, long long q_stride, void* o
   kv.head_stride = page_size * head_dim; kv.page_size = page_size; kv.page_shift = 0;
   while ((1 << kv.page_shift) < page_size) ++kv.page_shift;
   AttnBatch b{block_tables, bt_stride, tile_entry, tile_q0, entry_q_start, entry_q_len, entry_ctx_start};
-  AttnOptions opt{v_dim, page_size * v_dim, softcap, keep_first, sink, gate, gate_parts, gate_part_stride, gate_stride};
+  if (q_temp_every < 0 || (dist_r1 != nullptr) != (dist_r2 != nullptr)) return IFX_ERR_UNSUPPORTED;
+  AttnOptions opt{v_dim, page_size * v_dim, softcap, keep_first, sink, gate, gate_parts, gate_part_stride, gate_stride,
+                  q_temp_coef, q_temp_every, dist_r1, dist_r2, sink_value};
   if (single_tokens) {            // every tile is one token (tile_q0 = its place in its entry): the kernel for those
     if (dtype == IFX_F32)
       return dispatch_single<float>(q, q_stride, out, out_stride, kv, b, n_tiles, n_heads, n_kv, head_dim, scale, window, opt, stream);
@@ -422,6 +447,22 @@ IFX_API int ifx_attn_paged_generic_ex(const void* q, long long q_stride, void* o
   if (dtype == IFX_BF16)
     return dispatch_generic<bf16>(q, q_stride, out, out_stride, kv, b, n_tiles, n_heads, n_kv, head_dim, scale, window, opt, stream);
   return IFX_ERR_UNSUPPORTED;
+}
+
+IFX_API int ifx_attn_paged_generic_ex(const void* q, long long q_stride, void* out, long long out_stride, int dtype,
+                                      void* k_layer, void* v_layer, long long page_stride, int page_size,
+                                      const int* block_tables, int bt_stride,
+                                      const int* tile_entry, const int* tile_q0, int n_tiles,
+                                      const int* entry_q_start, const int* entry_q_len, const int* entry_ctx_start,
+                                      int n_heads, int n_kv, int head_dim, float scale, int window,
+                                      int v_dim, float softcap, int keep_first, int sink,
+                                      const float* gate, int gate_parts, long long gate_part_stride, int gate_stride,
+                                      int single_tokens, cudaStream_t stream) {
+  return ifx_attn_paged_generic_ex2(q, q_stride, out, out_stride, dtype, k_layer, v_layer, page_stride, page_size,
+                                    block_tables, bt_stride, tile_entry, tile_q0, n_tiles, entry_q_start, entry_q_len,
+                                    entry_ctx_start, n_heads, n_kv, head_dim, scale, window, v_dim, softcap, keep_first,
+                                    sink, gate, gate_parts, gate_part_stride, gate_stride, single_tokens, 0.0f, 0,
+                                    nullptr, nullptr, nullptr, stream);
 }
 
 IFX_API int ifx_attn_paged_generic(const void* q, long long q_stride, void* out, long long out_stride, int dtype,

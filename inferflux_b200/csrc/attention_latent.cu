@@ -63,17 +63,20 @@ struct LatentBatch {
 // Where a (token, head) vector of `rank` elements lies: token * row + head * head elements from the start.
 struct HeadLayout { long long row, head; };
 
-// q float32, out of the cache's type T, each laid out by its HeadLayout.  cache: the run's latents of page 0,
-// [slot][rank] within a page.
+// q float32, out of the cache's type T, each laid out by its HeadLayout.  cache: the run's rows of page 0,
+// [slot][kw] within a page.  A cached row is kw wide: its first `rank` elements are the latent, which serves as
+// key and as value; the other kw - rank (a rotated key part that all heads share, say) enter the scores only.
+// Queries are kw wide, results rank wide.  window > 0 hides keys j <= p - window; sink ([n_heads] or null) puts
+// one more term exp(sink[head]) without a value into the softmax's denominator.
 template <typename T, int NACC>
 __global__ void __launch_bounds__(256)
 attn_latent_paged_kernel(const float* __restrict__ q, HeadLayout ql, T* __restrict__ out, HeadLayout ol,
                          const T* __restrict__ cache, long long page_stride, int page_size, int page_shift,
-                         LatentBatch b, int rank, float scale) {
+                         LatentBatch b, int rank, int kw, float scale, int window, const float* __restrict__ sink) {
   pdl_enter();
   extern __shared__ float smem[];
-  float* qs = smem;                               // [LQ][rank]
-  float* cs = qs + LQ * rank;                     // [LKEYS][rank + 1]
+  float* qs = smem;                               // [LQ][kw]
+  float* cs = qs + LQ * kw;                       // [LKEYS][kw + 1]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int tile = blockIdx.x, head = blockIdx.y;
   const int e = b.tile_entry[tile];
@@ -84,38 +87,41 @@ attn_latent_paged_kernel(const float* __restrict__ q, HeadLayout ql, T* __restri
   const int pos0 = b.entry_ctx_start[e] + q0;
   const int* bt = b.block_tables + (size_t)e * b.bt_stride;
 
-  for (int idx = tid; idx < LQ * rank; idx += blockDim.x) {
-    const int r = idx / rank, d = idx - r * rank;
+  for (int idx = tid; idx < LQ * kw; idx += blockDim.x) {
+    const int r = idx / kw, d = idx - r * kw;
     qs[idx] = r < rows ? q[(size_t)(tok0 + r) * ql.row + (size_t)head * ql.head + d] : 0.0f;
   }
 
   const int r0 = warp * 2, r1 = r0 + 1;
-  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+  // a sink is a key without a value: the running maximum starts at its score and the sum at exp(0)
+  const float sink0 = sink ? sink[head] : -INFINITY;
+  float m[2] = {sink0, sink0}, l[2] = {sink ? 1.0f : 0.0f, sink ? 1.0f : 0.0f};
   float o[2][NACC];
 #pragma unroll
   for (int a = 0; a < NACC; ++a) { o[0][a] = 0.0f; o[1][a] = 0.0f; }
 
   const int kend = pos0 + rows - 1;               // last key any row of the tile may see
-  for (int k0 = 0; k0 <= kend; k0 += LKEYS) {
+  const int kstart = window > 0 ? max(0, pos0 - window + 1) & ~(LKEYS - 1) : 0;
+  for (int k0 = kstart; k0 <= kend; k0 += LKEYS) {
     __syncthreads();
-    for (int idx = tid; idx < LKEYS * rank; idx += blockDim.x) {
-      const int j = idx / rank, d = idx - j * rank;
+    for (int idx = tid; idx < LKEYS * kw; idx += blockDim.x) {
+      const int j = idx / kw, d = idx - j * kw;
       const int key = k0 + j;
       float c = 0.0f;
       if (key <= kend) {
         const int page = bt[key >> page_shift];
-        if (page >= 0) c = Num<T>::to_f(cache[(size_t)page * page_stride + (size_t)(key & (page_size - 1)) * rank + d]);
+        if (page >= 0) c = Num<T>::to_f(cache[(size_t)page * page_stride + (size_t)(key & (page_size - 1)) * kw + d]);
       }
-      cs[j * (rank + 1) + d] = c;
+      cs[j * (kw + 1) + d] = c;
     }
     __syncthreads();
     if (r0 < rows) {                               // warp-uniform
       const bool two = r1 < rows;
-      const float* cr = cs + lane * (rank + 1);
-      const float* qa = qs + r0 * rank;
-      const float* qb = qs + r1 * rank;
+      const float* cr = cs + lane * (kw + 1);
+      const float* qa = qs + r0 * kw;
+      const float* qb = qs + r1 * kw;
       float s0 = 0.0f, s1 = 0.0f;
-      for (int d = 0; d < rank; ++d) {
+      for (int d = 0; d < kw; ++d) {
         const float cd = cr[d];
         s0 = fmaf(qa[d], cd, s0);
         s1 = fmaf(qb[d], cd, s1);
@@ -125,7 +131,7 @@ attn_latent_paged_kernel(const float* __restrict__ q, HeadLayout ql, T* __restri
       for (int rr = 0; rr < 2; ++rr) {
         if (rr == 1 && !two) break;
         const int p = pos0 + r0 + rr;
-        const bool visible = key <= p;
+        const bool visible = key <= p && (window <= 0 || key > p - window);
         const float s = visible ? (rr ? s1 : s0) * scale : -INFINITY;
         const float m_new = fmaxf(m[rr], warp_max(s));
         if (m_new == -INFINITY) continue;          // nothing visible to this row yet (warp-uniform)
@@ -141,7 +147,7 @@ attn_latent_paged_kernel(const float* __restrict__ q, HeadLayout ql, T* __restri
 #pragma unroll
           for (int a = 0; a < NACC; ++a) {
             const int d = lane + 32 * a;
-            if (d < rank) o[rr][a] = fmaf(pjj, cs[j * (rank + 1) + d], o[rr][a]);
+            if (d < rank) o[rr][a] = fmaf(pjj, cs[j * (kw + 1) + d], o[rr][a]);
           }
         }
       }
@@ -163,8 +169,9 @@ attn_latent_paged_kernel(const float* __restrict__ q, HeadLayout ql, T* __restri
 
 template <typename T, int NACC>
 int launch_latent(const float* q, HeadLayout ql, void* out, HeadLayout ol, const void* cache, long long page_stride,
-                  int page_size, LatentBatch b, int n_tiles, int n_heads, int rank, float scale, cudaStream_t stream) {
-  const size_t smem = ((size_t)LQ * rank + (size_t)LKEYS * (rank + 1)) * sizeof(float);
+                  int page_size, LatentBatch b, int n_tiles, int n_heads, int rank, int kw, float scale, int window,
+                  const float* sink, cudaStream_t stream) {
+  const size_t smem = ((size_t)LQ * kw + (size_t)LKEYS * (kw + 1)) * sizeof(float);
   auto kern = attn_latent_paged_kernel<T, NACC>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -173,15 +180,16 @@ int launch_latent(const float* q, HeadLayout ql, void* out, HeadLayout ol, const
   int page_shift = 0;
   while ((1 << page_shift) < page_size) ++page_shift;
   const int rc = launch_pdl(kern, dim3(n_tiles, n_heads), dim3(256), smem, stream, q, ql, (T*)out, ol, (const T*)cache,
-                            page_stride, page_size, page_shift, b, rank, scale);
+                            page_stride, page_size, page_shift, b, rank, kw, scale, window, sink);
   return rc ? rc : IFX_LAUNCH_CHECK();
 }
 
 template <typename T>
 int dispatch_latent(const float* q, HeadLayout ql, void* out, HeadLayout ol, const void* cache, long long page_stride,
-                    int page_size, LatentBatch b, int n_tiles, int n_heads, int rank, float scale, cudaStream_t stream) {
+                    int page_size, LatentBatch b, int n_tiles, int n_heads, int rank, int kw, float scale, int window,
+                    const float* sink, cudaStream_t stream) {
   const int nacc = (rank + 31) / 32;
-#define IFX_LAT(N) return launch_latent<T, N>(q, ql, out, ol, cache, page_stride, page_size, b, n_tiles, n_heads, rank, scale, stream)
+#define IFX_LAT(N) return launch_latent<T, N>(q, ql, out, ol, cache, page_stride, page_size, b, n_tiles, n_heads, rank, kw, scale, window, sink, stream)
   if (nacc <= 1) IFX_LAT(1);
   if (nacc <= 2) IFX_LAT(2);
   if (nacc <= 4) IFX_LAT(4);
@@ -189,6 +197,53 @@ int dispatch_latent(const float* q, HeadLayout ql, void* out, HeadLayout ol, con
   if (nacc <= 16) IFX_LAT(16);
   IFX_LAT(32);
 #undef IFX_LAT
+}
+
+// A token's stacked float32 sums [q heads (each `dim` plain then `rot` rotating columns) | latent (kv_rank) |
+// rotating key part (rot)] become what the step needs: the plain query parts side by side in the engine's type
+// (the operand of the product with the keys' up-projection), the rotated query parts as float32 in the last
+// `rot` columns of every head's (kv_rank + rot)-wide query row, and in the token's place in the paged cache the
+// latent, divided by its root mean square and multiplied by its weight, followed by the rotated key part.
+// Neighbouring pairs (2i, 2i + 1) rotate by cos/sin [N, rot / 2].
+template <typename T>
+__global__ void latent_rope_prep_kernel(const float* __restrict__ p, long long p_stride, const float* __restrict__ wkv,
+                                        float eps, int n_heads, int dim, int rot, int kv_rank,
+                                        const float* __restrict__ cosv, const float* __restrict__ sinv,
+                                        T* __restrict__ q_plain, float* __restrict__ q_rows, long long q_row, long long q_head,
+                                        T* __restrict__ cache, long long page_stride, int page_size,
+                                        const int* __restrict__ slot_map) {
+  pdl_enter();
+  __shared__ float red[32];
+  const int row = blockIdx.x, half = rot >> 1;
+  const float* pr = p + (size_t)row * p_stride;
+  const float* cr = cosv + (size_t)row * half;
+  const float* sr = sinv + (size_t)row * half;
+  const int hw = dim + rot;
+  for (int i = threadIdx.x; i < n_heads * dim; i += blockDim.x) {
+    const int h = i / dim, d = i - h * dim;
+    q_plain[(size_t)row * n_heads * dim + i] = Num<T>::from_f(pr[h * hw + d]);
+  }
+  for (int i = threadIdx.x; i < n_heads * half; i += blockDim.x) {
+    const int h = i / half, j = i - h * half;
+    const float u = pr[h * hw + dim + 2 * j], v = pr[h * hw + dim + 2 * j + 1];
+    float* dst = q_rows + (size_t)row * q_row + (size_t)h * q_head + kv_rank + 2 * j;
+    dst[0] = u * cr[j] - v * sr[j];
+    dst[1] = v * cr[j] + u * sr[j];
+  }
+  const float* pk = pr + (size_t)n_heads * hw;
+  float sq = 0.0f;
+  for (int i = threadIdx.x; i < kv_rank; i += blockDim.x) sq = fmaf(pk[i], pk[i], sq);
+  const float rk = 1.0f / sqrtf(block_sum(sq, red) / (float)kv_rank + eps);
+  const int slot = slot_map[row];
+  if (slot >= 0) {
+    T* c = cache + (size_t)(slot / page_size) * page_stride + (size_t)(slot % page_size) * (kv_rank + rot);
+    for (int i = threadIdx.x; i < kv_rank; i += blockDim.x) c[i] = Num<T>::from_f(pk[i] * rk * wkv[i]);
+    for (int j = threadIdx.x; j < half; j += blockDim.x) {
+      const float u = pk[kv_rank + 2 * j], v = pk[kv_rank + 2 * j + 1];
+      c[kv_rank + 2 * j] = Num<T>::from_f(u * cr[j] - v * sr[j]);
+      c[kv_rank + 2 * j + 1] = Num<T>::from_f(v * cr[j] + u * sr[j]);
+    }
+  }
 }
 }  // namespace
 
@@ -216,7 +271,7 @@ IFX_API int ifx_latent_prep(const float* p, long long p_stride, const float* wq,
 }
 
 namespace {
-// out[t, h, :] = in[t, h, :] * gate[t, h], from rows laid out by `il` into contiguous [N, heads * width] rows of
+// out[t, h, :] = in[t, h, :] * gate[t, h] (gate null: times 1), from rows laid out by `il` into contiguous [N, heads * width] rows of
 // the engine's type: the per-head output gate, the rounding and the gathering of the heads in one pass.  With
 // row_entry the kernel takes only the rows of entries that bring more than one token (prompt == 1) or exactly
 // one (prompt == 0) and leaves the others as they are.
@@ -230,7 +285,7 @@ __global__ void gate_heads_kernel(const TI* __restrict__ in, HeadLayout il, cons
   const int total = n_heads * width;
   for (int i = threadIdx.x; i < total; i += blockDim.x) {
     const int h = i / width, d = i - h * width;
-    out[(size_t)row * out_stride + i] = Num<TO>::from_f(Num<TI>::to_f(in[(size_t)row * il.row + (size_t)h * il.head + d]) * gate[(size_t)row * n_heads + h]);
+    out[(size_t)row * out_stride + i] = Num<TO>::from_f(Num<TI>::to_f(in[(size_t)row * il.row + (size_t)h * il.head + d]) * (gate ? gate[(size_t)row * n_heads + h] : 1.0f));
   }
 }
 
@@ -289,21 +344,55 @@ IFX_API int ifx_gather_latents(const void* cache, int dtype, long long page_stri
   return rc ? rc : IFX_LAUNCH_CHECK();
 }
 
-// Query tiles are 16 tokens of one entry: tile_entry / tile_q0 list them.  rank: 1..1024.  q float32 and out (of
-// the cache's type) hold a (token, head) vector at token * row + head * head elements.
+// Query tiles are 16 tokens of one entry: tile_entry / tile_q0 list them.  kw: 1..1024, rank <= kw.  q float32 (kw
+// wide) and out (rank wide, of the cache's type) hold a (token, head) vector at token * row + head * head elements.
+IFX_API int ifx_attn_latent_paged_ex(const float* q, long long q_row, long long q_head, void* out, long long o_row,
+                                     long long o_head, const void* cache, int cache_dtype, long long page_stride,
+                                     int page_size, const int* block_tables, int bt_stride, const int* tile_entry,
+                                     const int* tile_q0, int n_tiles, const int* entry_q_start, const int* entry_q_len,
+                                     const int* entry_ctx_start, int n_heads, int rank, int kw, float scale, int window,
+                                     const float* sink, cudaStream_t stream) {
+  if (n_tiles <= 0) return 0;
+  if (rank < 1 || kw < rank || kw > 1024 || n_heads < 1 || n_heads > 65535 || window < 0) return IFX_ERR_UNSUPPORTED;
+  if (page_size <= 0 || (page_size & (page_size - 1))) return IFX_ERR_UNSUPPORTED;
+  LatentBatch b{block_tables, bt_stride, tile_entry, tile_q0, entry_q_start, entry_q_len, entry_ctx_start};
+  HeadLayout ql{q_row, q_head}, ol{o_row, o_head};
+  if (cache_dtype == IFX_F32)
+    return dispatch_latent<float>(q, ql, out, ol, cache, page_stride, page_size, b, n_tiles, n_heads, rank, kw, scale, window, sink, stream);
+  if (cache_dtype == IFX_BF16)
+    return dispatch_latent<bf16>(q, ql, out, ol, cache, page_stride, page_size, b, n_tiles, n_heads, rank, kw, scale, window, sink, stream);
+  return IFX_ERR_UNSUPPORTED;
+}
+
 IFX_API int ifx_attn_latent_paged(const float* q, long long q_row, long long q_head, void* out, long long o_row,
                                   long long o_head, const void* cache, int cache_dtype, long long page_stride,
                                   int page_size, const int* block_tables, int bt_stride, const int* tile_entry,
                                   const int* tile_q0, int n_tiles, const int* entry_q_start, const int* entry_q_len,
                                   const int* entry_ctx_start, int n_heads, int rank, float scale, cudaStream_t stream) {
-  if (n_tiles <= 0) return 0;
-  if (rank < 1 || rank > 1024 || n_heads < 1 || n_heads > 65535) return IFX_ERR_UNSUPPORTED;
-  if (page_size <= 0 || (page_size & (page_size - 1))) return IFX_ERR_UNSUPPORTED;
-  LatentBatch b{block_tables, bt_stride, tile_entry, tile_q0, entry_q_start, entry_q_len, entry_ctx_start};
-  HeadLayout ql{q_row, q_head}, ol{o_row, o_head};
-  if (cache_dtype == IFX_F32)
-    return dispatch_latent<float>(q, ql, out, ol, cache, page_stride, page_size, b, n_tiles, n_heads, rank, scale, stream);
-  if (cache_dtype == IFX_BF16)
-    return dispatch_latent<bf16>(q, ql, out, ol, cache, page_stride, page_size, b, n_tiles, n_heads, rank, scale, stream);
-  return IFX_ERR_UNSUPPORTED;
+  return ifx_attn_latent_paged_ex(q, q_row, q_head, out, o_row, o_head, cache, cache_dtype, page_stride, page_size,
+                                  block_tables, bt_stride, tile_entry, tile_q0, n_tiles, entry_q_start, entry_q_len,
+                                  entry_ctx_start, n_heads, rank, rank, scale, 0, nullptr, stream);
+}
+
+// p float32 [N, n_heads * (dim + rot) + kv_rank + rot] (row stride p_stride); q_plain [N, n_heads * dim] and the
+// cache (rows of kv_rank + rot) are of dtype; q_rows float32, a (token, head) row at token * q_row + head * q_head.
+IFX_API int ifx_latent_rope_prep(const float* p, long long p_stride, const float* wkv, float eps, int n_heads, int dim,
+                                 int rot, int kv_rank, const float* cosv, const float* sinv, void* q_plain, float* q_rows,
+                                 long long q_row, long long q_head, void* cache, int dtype, long long page_stride,
+                                 int page_size, const int* slot_map, int n_rows, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (n_heads < 1 || dim < 0 || rot < 0 || (rot & 1) || kv_rank < 1 || page_size < 1) return IFX_ERR_UNSUPPORTED;
+  const int widest = n_heads * dim > kv_rank ? n_heads * dim : kv_rank;
+  int threads = 64;
+  while (threads < 1024 && threads * 4 < widest) threads <<= 1;
+  int rc;
+  if (dtype == IFX_F32)
+    rc = launch_pdl(latent_rope_prep_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, p, p_stride, wkv, eps, n_heads, dim,
+                    rot, kv_rank, cosv, sinv, (float*)q_plain, q_rows, q_row, q_head, (float*)cache, page_stride, page_size, slot_map);
+  else if (dtype == IFX_BF16)
+    rc = launch_pdl(latent_rope_prep_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, p, p_stride, wkv, eps, n_heads, dim,
+                    rot, kv_rank, cosv, sinv, (bf16*)q_plain, q_rows, q_row, q_head, (bf16*)cache, page_stride, page_size, slot_map);
+  else
+    return IFX_ERR_UNSUPPORTED;
+  return rc ? rc : IFX_LAUNCH_CHECK();
 }

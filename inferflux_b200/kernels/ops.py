@@ -185,6 +185,23 @@ def _lib():
         lib.ifx_qkv_norm_rope_write.argtypes = [c_void_p, c_int, c_ll, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
                                                 c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                                 c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_void_p]
+        lib.ifx_add_group_rmsnorm.argtypes = [c_void_p, c_void_p, c_int, c_ll, c_float, c_void_p, c_int, c_ll, c_float, c_int,
+                                              c_void_p, c_float, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]
+        lib.ifx_glu_clamped.argtypes = [c_void_p, c_int, c_ll, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_float,
+                                        c_void_p]
+        lib.ifx_gla_scan.argtypes = [c_void_p, c_ll, c_int, c_int, c_int, c_void_p, c_ll, c_void_p, c_float, c_float, c_void_p,
+                                     c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_ll, c_int, c_int, c_int, c_void_p]
+        lib.ifx_attn_paged_generic_ex2.argtypes = list(lib.ifx_attn_paged_generic_ex.argtypes[:-1]) + [
+            c_float, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
+        lib.ifx_attn_latent_paged_ex.argtypes = [c_void_p, c_ll, c_ll, c_void_p, c_ll, c_ll, c_void_p, c_int, c_ll, c_int,
+                                                 c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                                 c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p]
+        lib.ifx_latent_rope_prep.argtypes = [c_void_p, c_ll, c_void_p, c_float, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                             c_void_p, c_void_p, c_ll, c_ll, c_void_p, c_int, c_ll, c_int, c_void_p, c_int,
+                                             c_void_p]
+        for name in ("ifx_add_group_rmsnorm", "ifx_glu_clamped", "ifx_gla_scan", "ifx_attn_paged_generic_ex2",
+                     "ifx_attn_latent_paged_ex", "ifx_latent_rope_prep"):
+            getattr(lib, name).restype = c_int
         for name in ("ifx_activation", "ifx_causal_conv", "ifx_ssm_scan", "ifx_gated_group_norm", "ifx_delta_rule_scan",
                      "ifx_head_norm_gate", "ifx_qkv_norm_rope_write"):
             getattr(lib, name).restype = c_int
@@ -1050,26 +1067,57 @@ def _head_layout(t: torch.Tensor, n_heads: int, width: int, what: str):
 def attn_latent_paged(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, page_stride: int, page_size: int,
                       block_tables: torch.Tensor, tile_entry: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int,
                       entry_q_start: torch.Tensor, entry_q_len: torch.Tensor, entry_ctx_start: torch.Tensor,
-                      scale: float) -> torch.Tensor:
+                      scale: float, window: int = 0, sink: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal attention of new tokens over the cached latents, which serve as
-    keys and as values: q float32 ``[N, heads, rank]`` (the queries moved into
-    the latent space; any view whose vectors are contiguous), out of the same
-    shape in the cache's type (the weighted sums of the latents).  Query tiles
-    of 16 tokens are listed by tile_entry / tile_q0."""
+    keys and as values: q float32 ``[N, heads, kw]`` (the queries moved into
+    the latent space; any view whose vectors are contiguous), out ``[N, heads,
+    rank]`` in the cache's type (the weighted sums of the latents).  A cached
+    row is ``kw >= rank`` wide; what lies behind the latent (a rotated key part
+    shared by the heads) enters the scores only.  ``window`` > 0 hides keys j
+    <= p - window; ``sink`` float32 ``[heads]`` adds ``exp(sink[h])`` to the
+    softmax's denominator.  Query tiles of 16 tokens are listed by tile_entry /
+    tile_q0."""
     _need(block_tables.dtype == torch.int32 and block_tables.dim() == 2 and block_tables.stride(1) == 1,
           "attn_latent: block_tables int32 [R, B]")
     for t in (tile_entry, tile_q0, entry_q_start, entry_q_len, entry_ctx_start):
         _need(t.dtype == torch.int32, "attn_latent: int32 metadata")
-    _need(q.dtype == torch.float32 and out.dtype == cache.dtype and q.shape == out.shape,
-          "attn_latent: q float32, out of the cache's type, same shape")
-    n_heads, rank = q.shape[1], q.shape[2]
-    _need(1 <= rank <= 1024, f"attn_latent: rank {rank} is outside 1..1024")
-    (q_row, q_head), (o_row, o_head) = _head_layout(q, n_heads, rank, "attn_latent q"), _head_layout(out, n_heads, rank, "attn_latent out")
-    _check(_lib().ifx_attn_latent_paged(_ptr(q), q_row, q_head, _ptr(out), o_row, o_head, _ptr(cache), _code(cache),
-                                        page_stride, page_size, _ptr(block_tables), block_tables.stride(0), _ptr(tile_entry),
-                                        _ptr(tile_q0), n_tiles, _ptr(entry_q_start), _ptr(entry_q_len),
-                                        _ptr(entry_ctx_start), n_heads, rank, float(scale), _stream()), "attn_latent_paged")
+    _need(q.dtype == torch.float32 and out.dtype == cache.dtype and q.shape[:2] == out.shape[:2] and out.shape[2] <= q.shape[2],
+          "attn_latent: q float32 [N, heads, kw], out [N, heads, rank <= kw] of the cache's type")
+    n_heads, kw, rank = q.shape[1], q.shape[2], out.shape[2]
+    _need(1 <= kw <= 1024, f"attn_latent: width {kw} is outside 1..1024")
+    _need(sink is None or (sink.dtype == torch.float32 and sink.is_contiguous() and sink.numel() == n_heads), "attn_latent: sink float32 [heads]")
+    (q_row, q_head), (o_row, o_head) = _head_layout(q, n_heads, kw, "attn_latent q"), _head_layout(out, n_heads, rank, "attn_latent out")
+    _check(_lib().ifx_attn_latent_paged_ex(_ptr(q), q_row, q_head, _ptr(out), o_row, o_head, _ptr(cache), _code(cache),
+                                           page_stride, page_size, _ptr(block_tables), block_tables.stride(0), _ptr(tile_entry),
+                                           _ptr(tile_q0), n_tiles, _ptr(entry_q_start), _ptr(entry_q_len),
+                                           _ptr(entry_ctx_start), n_heads, rank, kw, float(scale), int(window), _ptr(sink),
+                                           _stream()), "attn_latent_paged")
     return out
+
+
+def latent_rope_prep(p: torch.Tensor, wkv: torch.Tensor, eps: float, n_heads: int, dim: int, rot: int, kv_rank: int,
+                     cos: torch.Tensor, sin: torch.Tensor, q_plain: torch.Tensor, q_rows: torch.Tensor, cache: torch.Tensor,
+                     page_stride: int, page_size: int, slot_map: torch.Tensor) -> None:
+    """p float32 ``[N, n_heads * (dim + rot) + kv_rank + rot]``: a token's query heads (``dim`` plain then ``rot``
+    rotating columns each), its latent and its rotating key part.  ``q_plain [N, n_heads * dim]`` (the cache's type)
+    takes the plain query parts; ``q_rows`` float32 ``[N, n_heads, kv_rank + rot]`` takes the rotated query parts in
+    its last ``rot`` columns; the cache row of the token (``kv_rank + rot`` wide, at ``slot_map``) takes the latent
+    divided by its root mean square times ``wkv`` and the rotated key part.  Neighbouring pairs ``(2i, 2i + 1)`` rotate
+    by ``cos``/``sin`` float32 ``[N, rot / 2]``."""
+    n = p.shape[0]
+    _need(p.dtype == torch.float32 and p.stride(1) == 1 and p.shape[1] == n_heads * (dim + rot) + kv_rank + rot,
+          "latent_rope_prep: p float32 [N, heads * (dim + rot) + kv_rank + rot]")
+    _need(wkv.dtype == torch.float32 and wkv.is_contiguous() and wkv.numel() == kv_rank, "latent_rope_prep: wkv float32 [kv_rank]")
+    _need(cos.dtype == torch.float32 and cos.is_contiguous() and sin.is_contiguous() and cos.shape == sin.shape
+          and tuple(cos.shape) == (n, rot // 2), "latent_rope_prep: cos/sin float32 [N, rot / 2]")
+    _need(q_plain.is_contiguous() and tuple(q_plain.shape) == (n, n_heads * dim) and q_plain.dtype == cache.dtype,
+          "latent_rope_prep: q_plain [N, heads * dim] of the cache's type")
+    _need(q_rows.dtype == torch.float32, "latent_rope_prep: q_rows float32")
+    q_row, q_head = _head_layout(q_rows, n_heads, kv_rank + rot, "latent_rope_prep q_rows")
+    _need(slot_map.dtype == torch.int32 and slot_map.numel() == n, "latent_rope_prep: slot_map int32 [N]")
+    _check(_lib().ifx_latent_rope_prep(_ptr(p), p.stride(0), _ptr(wkv), float(eps), n_heads, dim, rot, kv_rank, _ptr(cos),
+                                       _ptr(sin), _ptr(q_plain), _ptr(q_rows), q_row, q_head, _ptr(cache), _code(cache),
+                                       page_stride, page_size, _ptr(slot_map), n, _stream()), "latent_rope_prep")
 
 
 def gate_heads(x: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, row_entry: Optional[torch.Tensor] = None,
@@ -1080,8 +1128,8 @@ def gate_heads(x: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, row_entry
     row) and ``entry_q_len`` only the rows of entries with more than one token
     (``prompt_rows``) or with exactly one are written."""
     n, n_heads, width = x.shape
-    _need(gate.dtype == torch.float32 and gate.is_contiguous() and tuple(gate.shape) == (n, n_heads),
-          "gate_heads: gate float32 [N, heads]")
+    _need(gate is None or (gate.dtype == torch.float32 and gate.is_contiguous() and tuple(gate.shape) == (n, n_heads)),
+          "gate_heads: gate float32 [N, heads] (or None: the heads are gathered and rounded as they are)")
     _need(out.stride(1) == 1 and tuple(out.shape) == (n, n_heads * width), "gate_heads: out [N, heads * width], unit inner stride")
     row, head = _head_layout(x, n_heads, width, "gate_heads x")
     _check(_lib().ifx_gate_heads(_ptr(x), _code(x), row, head, _ptr(gate), _ptr(out), out.stride(0), _code(out), n, n_heads, width,
@@ -1261,15 +1309,23 @@ def attn_paged_options(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_laye
                        tile_q0: torch.Tensor, n_tiles: int, entry_q_start: torch.Tensor, entry_q_len: torch.Tensor,
                        entry_ctx_start: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, scale: float, window: int,
                        v_dim: int, softcap: float = 0.0, keep_first: int = 0, sink: bool = False,
-                       gate: Optional[torch.Tensor] = None, single_tokens: bool = False) -> torch.Tensor:
+                       gate: Optional[torch.Tensor] = None, single_tokens: bool = False, q_temp=None,
+                       distance_toll=None, sink_value: Optional[torch.Tensor] = None) -> torch.Tensor:
     """With ``single_tokens`` every listed tile is one token (``tile_q0`` = its place in its entry) and the kernel
     for single tokens runs (a block a token and head, its warps sharing the keys out).  Otherwise
     :func:`attn_paged_generic` with values ``v_dim`` wide, a cap on the scores (``softcap * tanh(s / softcap)``,
     0 = none), ``keep_first`` first tokens that stay visible behind the window, a sink (one more term ``exp(0)`` in
     the denominator) and an output gate: ``gate`` = float32 ``[N, W]`` or ``[P, N, W]`` sums whose first
-    ``n_heads * v_dim`` columns go through a sigmoid and multiply the result element by element."""
+    ``n_heads * v_dim`` columns go through a sigmoid and multiply the result element by element.
+    ``q_temp`` = ``(coef, every)``: the query at position p counts ``1 + coef * ln(floor((p + 1) / every) + 1)`` times;
+    ``distance_toll`` = ``(r1, r2)``, float32 ``[n_heads]`` each: the score of key j loses ``r1 * ln(1 + r2 * (p - j))``
+    (after the cap); ``sink_value`` float32 ``[n_heads]``: the sink's score per head instead of 0."""
     _need(block_tables.dtype == torch.int32 and block_tables.dim() == 2 and block_tables.stride(1) == 1,
           "attn: block_tables int32 [R, B]")
+    coef, every = (float(q_temp[0]), int(q_temp[1])) if q_temp else (0.0, 0)
+    r1, r2 = distance_toll if distance_toll else (None, None)
+    for t in (r1, r2, sink_value):
+        _need(t is None or (t.dtype == torch.float32 and t.is_contiguous() and t.numel() == n_heads), "attn: per-head numbers float32 [heads]")
     _need(out.is_contiguous() and out.dtype == q.dtype and k_layer.dtype == q.dtype and out.shape[1] == n_heads * v_dim, "attn: types")
     gp, g_parts, g_pstride, g_stride = None, 0, 0, 0
     if gate is not None:
@@ -1279,13 +1335,14 @@ def attn_paged_options(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_laye
             g_parts, g_pstride, g_stride = gate.shape[0], gate.stride(0), gate.stride(1)
         else:
             g_parts, g_pstride, g_stride = 1, 0, gate.stride(0)
-    _check(_lib().ifx_attn_paged_generic_ex(_ptr(q), q_stride, _ptr(out), out.stride(0), _code(q), _ptr(k_layer),
+    _check(_lib().ifx_attn_paged_generic_ex2(_ptr(q), q_stride, _ptr(out), out.stride(0), _code(q), _ptr(k_layer),
                                             _ptr(v_layer), page_stride, page_size, _ptr(block_tables),
                                             block_tables.stride(0), _ptr(tile_entry), _ptr(tile_q0), n_tiles,
                                             _ptr(entry_q_start), _ptr(entry_q_len), _ptr(entry_ctx_start),
                                             n_heads, n_kv, head_dim, float(scale), int(window), int(v_dim), float(softcap),
                                             int(keep_first), 1 if sink else 0, gp, g_parts, g_pstride, g_stride,
-                                            1 if single_tokens else 0, _stream()),
+                                            1 if single_tokens else 0, coef, every, _ptr(r1), _ptr(r2), _ptr(sink_value),
+                                            _stream()),
            "attn_paged_options")
     return out
 
@@ -1624,3 +1681,68 @@ def qkv_norm_rope_write(proj: torch.Tensor, wq: Optional[torch.Tensor], wk: Opti
                                           int(mix_mode), _ptr(mix_lambda), _ptr(v_first), _ptr(q_out), _code(q_out),
                                           _ptr(slot_map), _ptr(k_layer), _ptr(v_layer), page_stride, page_size, n,
                                           _stream()), "qkv_norm_rope_write")
+
+
+def add_group_rmsnorm(residual: torch.Tensor, a, weight: torch.Tensor, eps: float, groups: int, out: Optional[torch.Tensor],
+                      rows: Optional[torch.Tensor] = None, a_scale: float = 1.0, b=None, b_scale: float = 1.0) -> Optional[torch.Tensor]:
+    """``residual`` (float32 ``[N, H]``) ``+= a_scale * a + b_scale * b``; ``out`` = the sum with each of ``groups``
+    equal consecutive parts of a row divided by its own root mean square (eps inside the root), times ``weight``.
+    ``a`` and ``b`` are None, ``[N, H]`` or slices ``[P, N, H]`` (float32 or bfloat16, both of one type).  With
+    ``rows`` (int32) only those rows are normed into ``out [R, H]`` and the residual is left untouched."""
+    n, hidden = residual.shape
+    _need(residual.dtype == torch.float32 and residual.is_contiguous(), "add_group_rmsnorm: residual float32 contiguous")
+    _need(weight.dtype == torch.float32 and weight.numel() == hidden and groups >= 1 and hidden % groups == 0,
+          "add_group_rmsnorm: weight float32 [H], groups dividing H")
+    n_rows = rows.numel() if rows is not None else n
+    _need(rows is None or rows.dtype == torch.int32, "add_group_rmsnorm: rows int32")
+
+    def slices(t):
+        if t is None:
+            return None, 1, 0
+        _need(t.is_contiguous() and tuple(t.shape[-2:]) == (n, hidden) and t.dim() in (2, 3), "add_group_rmsnorm: addends [N, H] or [P, N, H]")
+        return _ptr(t), (t.shape[0] if t.dim() == 3 else 1), n * hidden
+    (pa, na, sa), (pb, nb, sb) = slices(a), slices(b)
+    if a is not None and b is not None:
+        _need(a.dtype == b.dtype, "add_group_rmsnorm: both addends of one type")
+    dd = _code(a if a is not None else b) if (a is not None or b is not None) else F32
+    if out is not None:
+        _need(out.is_contiguous() and tuple(out.shape) == (n_rows, hidden), "add_group_rmsnorm: out [rows, H]")
+    _check(_lib().ifx_add_group_rmsnorm(_ptr(residual), pa, na, sa, float(a_scale), pb, nb, sb, float(b_scale), dd, _ptr(weight),
+                                        float(eps), int(groups), _ptr(out), _code(out) if out is not None else F32, _ptr(rows),
+                                        n_rows, hidden, 0 if rows is not None else 1, _stream()), "add_group_rmsnorm")
+    return out
+
+
+def glu_clamped(z: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, limit: float, alpha: float = 1.702,
+                shift: float = 1.0) -> torch.Tensor:
+    """``z`` float32 ``[M, 2I]`` or slices ``[P, M, 2I]`` (gate columns first, then up): ``g = min(z_g + b_g, limit)``,
+    ``u = clamp(z_u + b_u, -limit, limit)``, ``out = g * sigmoid(alpha * g) * (u + shift)``."""
+    m, inter = out.shape
+    _need(z.dtype == torch.float32 and z.is_contiguous() and tuple(z.shape[-2:]) == (m, 2 * inter), "glu_clamped: z float32 [M, 2I]")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == 2 * inter), "glu_clamped: bias float32 [2I]")
+    _need(out.is_contiguous(), "glu_clamped: out contiguous")
+    parts = z.shape[0] if z.dim() == 3 else 1
+    _check(_lib().ifx_glu_clamped(_ptr(z), parts, m * 2 * inter, _ptr(bias), _ptr(out), _code(out), m, inter, float(limit),
+                                  float(alpha), float(shift), _stream()), "glu_clamped")
+    return out
+
+
+def gla_scan(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, z: torch.Tensor, z_bias: torch.Tensor, tau: float,
+             q_scale: float, state: torch.Tensor, entry_q_start: torch.Tensor, entry_q_len: torch.Tensor,
+             entry_slot: torch.Tensor, n_entries: int, out: torch.Tensor, heads: int, dim: int, vdim: int) -> torch.Tensor:
+    """Gated linear attention, float32.  Per head ``alpha = sigmoid(z + z_bias)^(1 / tau)`` (one per key channel),
+    ``S <- diag(alpha) S + k v^T``, ``o = S^T (q * q_scale)``.  ``proj`` float32 rows hold q, k (``heads * dim`` each)
+    and v (``heads * vdim``) from the given columns; ``z`` float32 rows ``[N, heads * dim]``; ``state [slots, heads,
+    dim, vdim]``; ``out`` float32 ``[N, heads * vdim]``."""
+    n = proj.shape[0]
+    _need(proj.dtype == torch.float32 and proj.stride(1) == 1 and z.dtype == torch.float32 and z.stride(1) == 1
+          and tuple(z.shape) == (n, heads * dim), "gla_scan: float32 rows")
+    _need(z_bias.dtype == torch.float32 and z_bias.is_contiguous() and z_bias.numel() == heads * dim, "gla_scan: z_bias float32 [heads * dim]")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, dim, vdim),
+          "gla_scan: state float32 [slots, heads, dim, vdim]")
+    _need(out.dtype == torch.float32 and out.stride(1) == 1 and tuple(out.shape) == (n, heads * vdim), "gla_scan: out")
+    _need(max(q_col, k_col) + heads * dim <= proj.shape[1] and v_col + heads * vdim <= proj.shape[1], "gla_scan: columns beyond the row")
+    _check(_lib().ifx_gla_scan(_ptr(proj), proj.stride(0), q_col, k_col, v_col, _ptr(z), z.stride(0), _ptr(z_bias),
+                               1.0 / float(tau), float(q_scale), _ptr(state), _ptr(entry_q_start), _ptr(entry_q_len),
+                               _ptr(entry_slot), n_entries, _ptr(out), out.stride(0), heads, dim, vdim, _stream()), "gla_scan")
+    return out

@@ -18,6 +18,7 @@ from .retention import Retention
 from .side_by_side import SideBySide
 from .state_space import Mamba2
 from .delta_rule import GeneralDelta
+from .gated_linear_attention import GatedLinearAttention
 
 __all__ = ["Part", "KVNeed", "StateNeed", "RunInfo", "Linear", "RMSNorm", "RotaryHalf",
            "GQAttention", "SwiGLU", "PreNormBlock", "TokenEmbedding", "LinearHead", "LayerNorm", "PolyNormFF",

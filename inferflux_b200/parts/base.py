@@ -79,6 +79,14 @@ class BranchMean:
         self.eps = eps
 
 
+class ScaledSum:
+    """A mixer's result given as a weighted sum of branches, ``s_a * a + s_b * b``, each branch the float32 sums of
+    one mixer (a tensor or :class:`PartialSums`).  The norm that takes it computes the sum while it adds to the stream."""
+
+    def __init__(self, terms):
+        self.terms = list(terms)                # [(sums, factor), ...]: two of them
+
+
 class NormedDelta:
     """A sublayer's result that is to be normed before it joins the stream: ``N(value) * weight`` with ``value``
     a tensor, :class:`PartialSums` or :class:`BranchMean`.  Blocks with a norm behind every sublayer hand this

@@ -21,7 +21,7 @@ import torch
 
 from ..config.registry import register_part
 from ..kernels import ops
-from .base import NormedDelta, PartialSums, RunInfo
+from .base import NormedDelta, PartialSums, RunInfo, ScaledSum
 from .linear import Linear
 from .norm import normed_sum
 
@@ -33,13 +33,15 @@ class PreNormBlock:
 
     family = "arrangement"
     roles = {"mixer": "mixer", "mixer_norm": "norm", "feed_forward": "feed_forward", "feed_forward_norm": "norm"}
-    optional_roles = frozenset()
+    optional_roles = frozenset({"feed_forward", "feed_forward_norm"})       # a layer may have no feed-forward
 
     def __init__(self, parts: Dict[str, object], position_name: Optional[str]):
         self.mixer = parts["mixer"]
         self.mixer_norm = parts["mixer_norm"]
-        self.feed_forward = parts["feed_forward"]
-        self.feed_forward_norm = parts["feed_forward_norm"]
+        self.feed_forward = parts.get("feed_forward")
+        self.feed_forward_norm = parts.get("feed_forward_norm")
+        if (self.feed_forward is None) != (self.feed_forward_norm is None):
+            raise ValueError("a prenorm block has a feed-forward with the norm ahead of it or neither")
         self.position_name = position_name
 
     def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], ctx, run: RunInfo) -> torch.Tensor:
@@ -48,6 +50,8 @@ class PreNormBlock:
         x = self.mixer_norm.forward(residual, delta)
         position = ctx.position_tables.get(self.position_name) if self.position_name else None
         a = self.mixer.forward(x, ctx, run, position)
+        if self.feed_forward is None:
+            return a
         x2 = self.feed_forward_norm.forward(residual, a)
         return self.feed_forward.forward(x2, ctx)
 
@@ -149,7 +153,11 @@ class JunctionBlock:
         self.junction = parts["junction"]
 
     def forward(self, residual: torch.Tensor, delta, ctx, run: RunInfo):
-        if delta is not None:
+        if isinstance(delta, ScaledSum):
+            for value, factor in delta.terms:
+                t = value.tensor.sum(0) if isinstance(value, PartialSums) else value
+                residual.add_(t, alpha=float(factor))
+        elif delta is not None:
             n_partials = 1
             if isinstance(delta, PartialSums):
                 delta, n_partials = delta.tensor, delta.count

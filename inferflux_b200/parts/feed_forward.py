@@ -147,6 +147,56 @@ class GeluMLP(Part):
         return self.down.forward(act, out_dtype=torch.float32, allow_partials=True, f32_sums=True)
 
 
+class ClampedGLU(Part):
+    """A gated feed-forward whose two inputs are clamped before they meet:
+
+        g = min(W_gate x + b_gate, limit)          u = clamp(W_up x + b_up, -limit, limit)
+        y = W_down ( g * sigmoid(alpha * g) * (u + shift) ) + b_down
+
+    Gate and up are one stacked projection whose sums stay float32; biases, clamps and the activation are one
+    kernel that rounds once into the engine's type.  params: ``hidden``, ``intermediate``, ``limit``, ``alpha``
+    (default 1.702), ``shift`` (default 1), ``bias`` (default true), ``name`` (tensors
+    ``<prefix>.<name>.{gate,up,down}`` and ``.{gate,up,down}.b``)."""
+
+    family = "feed_forward"
+
+    def __init__(self, params, prefix, dtype, device):
+        super().__init__(params, prefix, dtype, device)
+        self.hidden, self.intermediate = int(params["hidden"]), int(params["intermediate"])
+        self.limit = float(params["limit"])
+        self.alpha, self.shift = float(params.get("alpha", 1.702)), float(params.get("shift", 1.0))
+        self.has_bias = bool(params.get("bias", True))
+        self.gate_up: Linear = None
+        self.gate_up_bias: torch.Tensor = None
+        self.down: Linear = None
+
+    @classmethod
+    def weight_specs(cls, params: Dict[str, Any], prefix: str) -> List[WeightSpec]:
+        h, i = int(params["hidden"]), int(params["intermediate"])
+        n = lambda leaf: cls.full_name(prefix, params, leaf)
+        specs = [WeightSpec(n("gate"), (i, h), MATRIX), WeightSpec(n("up"), (i, h), MATRIX), WeightSpec(n("down"), (h, i), MATRIX)]
+        if params.get("bias", True):
+            specs += [WeightSpec(n("gate.b"), (i,), VECTOR), WeightSpec(n("up.b"), (i,), VECTOR), WeightSpec(n("down.b"), (h,), VECTOR)]
+        return specs
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        n = lambda leaf: self.full_name(self.prefix, self.params, leaf)
+        gate, up = tensors.pop(n("gate")), tensors.pop(n("up"))
+        if gate.dtype != up.dtype:
+            gate, up = gate.float(), up.float()
+        self.gate_up = Linear(torch.cat([gate, up], dim=0))
+        del gate, up
+        if self.has_bias:
+            self.gate_up_bias = torch.cat([tensors.pop(n("gate.b")).float(), tensors.pop(n("up.b")).float()]).contiguous()
+        self.down = Linear(tensors.pop(n("down")), tensors.pop(n("down.b")) if self.has_bias else None)
+
+    def forward(self, x: torch.Tensor, ctx):
+        z = self.gate_up.forward(x, out_dtype=torch.float32, allow_partials=True, f32_sums=True)
+        act = torch.empty((x.shape[0], self.intermediate), dtype=x.dtype, device=x.device)
+        ops.glu_clamped(z.tensor if isinstance(z, PartialSums) else z, self.gate_up_bias, act, self.limit, self.alpha, self.shift)
+        return self.down.forward(act, out_dtype=torch.float32, allow_partials=True, f32_sums=True)
+
+
 class SquaredReluMLP(Part):
     """``down( relu(up(x))^2 )``, no biases.  The up projection leaves float32 sums; the activation rounds once into
     the engine's type.  params: ``hidden``, ``intermediate``, ``name`` (tensors ``<prefix>.<name>.{up,down}``)."""
@@ -268,6 +318,7 @@ class RoutedExperts(Part):
 
 register_part("feed_forward", "swiglu", SwiGLU)
 register_part("feed_forward", "gelu_mlp", GeluMLP)
+register_part("feed_forward", "clamped_glu", ClampedGLU)
 register_part("feed_forward", "routed_experts", RoutedExperts)
 register_part("feed_forward", "relu2_mlp", SquaredReluMLP)
 register_part("feed_forward", "polynorm", PolyNormFF)

@@ -8,6 +8,8 @@ renewed from itself and from the embedding output,
 ``t`` being the number of the pass (the run's parameter ``pass``) and ``x0``
 the stream as the embedding left it.  The half of the product that reads x0
 is the same in every pass and is made once per step; the sum is float32.
+
+``add_embedding``: ``x <- x + x0``, nothing else.
 """
 from __future__ import annotations
 
@@ -60,4 +62,15 @@ class LoopEntry(Part):
         ops.add_rows_vector(y, base, self.step[int(run.params["pass"])], residual)
 
 
+class AddEmbedding(Part):
+    """``x <- x + x0`` with ``x0`` the stream as the embedding left it: where a later pass over a stretch of layers
+    begins, the tokens' embeddings join the stream again.  No weights; params: none."""
+
+    family = "junction"
+
+    def forward(self, residual: torch.Tensor, ctx, run: RunInfo) -> None:
+        ops.add_into(residual, ctx.embedding_output, 1)
+
+
 register_part("junction", "loop_entry", LoopEntry)
+register_part("junction", "add_embedding", AddEmbedding)

@@ -14,6 +14,19 @@ works on latents alone and all heads of a token read the same cached rows.
 The three projections of x are stacked at load into one product whose sums
 stay float32; both unit-rms norms, the cache write and the gates' sigmoid are
 one kernel; scores, softmax and the weighted sums are float32.
+
+Options, each a parameter: ``q_rank`` 0 = the queries are one projection of x (``q``) without a latent of their
+own; ``gate`` false = no output gates; ``rot_dim`` > 0 = every query head has ``rot_dim`` more columns behind its
+``dim`` plain ones, the down projection ``dkv`` has ``rot_dim`` more rows behind the latent's (not normed), and
+both are rotated by the layer's position table in neighbouring pairs ``(2i, 2i + 1)``: one rotated key part per
+token, shared by all heads, so that
+
+    score_h(i, j) = (q_plain_h(i) . (Uk_h c_j) + q_rot_h(i) . k_rot(j)) * scale;
+
+the cached row is then ``[c | k_rot]``, ``kv_rank + rot_dim`` wide, the kernel's query ``[Uk_h^T q_plain_h | q_rot_h]``,
+and the value still the latent alone.  ``window`` > 0 = key j is visible to position p iff ``0 <= p - j < window``
+(pages behind the window go back to the pool); ``sink`` = a stored number per head whose exponential joins the
+softmax's denominator, without a key or a value.
 """
 from __future__ import annotations
 
@@ -69,7 +82,10 @@ class PromptStep:
 class LatentAttention(Part):
     """params: ``hidden``, ``heads``, ``dim`` (of queries and keys), ``vdim``,
     ``kv_rank``, ``q_rank``, ``scale``, ``eps`` (of the two unit-rms norms),
-    ``name`` (tensors ``<prefix>.<name>.{dq,dq.norm,uq,dkv,dkv.norm,uk,uv,g,o}``)."""
+    ``gate`` (default true), ``rot_dim``, ``window``, ``sink`` (defaults 0, 0, false),
+    ``name`` (tensors ``<prefix>.<name>.{dq,dq.norm,uq,dkv,dkv.norm,uk,uv,g,o}``; with
+    ``q_rank`` 0 ``q`` instead of ``dq``, ``dq.norm`` and ``uq``; ``sink`` ``[heads]``).
+    Position (with ``rot_dim``): a pair ``(cos, sin)`` of float32 ``[N, rot_dim / 2]`` tensors."""
 
     family = "mixer"
 
@@ -78,10 +94,21 @@ class LatentAttention(Part):
         p = params
         self.hidden, self.heads = int(p["hidden"]), int(p["heads"])
         self.dim, self.vdim = int(p["dim"]), int(p["vdim"])
-        self.kv_rank, self.q_rank = int(p["kv_rank"]), int(p["q_rank"])
+        self.kv_rank, self.q_rank = int(p["kv_rank"]), int(p.get("q_rank") or 0)
         self.scale, self.eps = float(p["scale"]), float(p["eps"])
+        self.gated = bool(p.get("gate", True))
+        self.rot_dim, self.window, self.has_sink = int(p.get("rot_dim") or 0), int(p.get("window") or 0), bool(p.get("sink"))
+        self.width = self.kv_rank + self.rot_dim        # of a cached row and of the kernel's queries
+        self.plain = self.q_rank > 0 and self.gated and not (self.rot_dim or self.window or self.has_sink)
+        if self.rot_dim % 2:
+            raise ValueError(f"latent_attention: rot_dim {self.rot_dim} must be even")
+        if self.rot_dim and self.q_rank:
+            raise ValueError("latent_attention: a rotated part and a query latent are not built together")
+        if not self.q_rank and self.gated:
+            raise ValueError("latent_attention: output gates without a query latent are not built")
+        self.sink: torch.Tensor = None
         # layers of the same sizes share a step's description
-        self.describe_key = f"latent_attention/{self.heads}/{self.dim}/{self.vdim}/{self.kv_rank}"
+        self.describe_key = f"latent_attention/{self.heads}/{self.dim}/{self.vdim}/{self.kv_rank}/{self.plain}"
         self.ukv: Linear = None             # [uk; uv] stacked, for steps that form keys and values
         if not 1 <= self.kv_rank <= 1024:
             raise ValueError(f"kv_rank {self.kv_rank} is outside 1..1024")
@@ -93,8 +120,14 @@ class LatentAttention(Part):
 
     @classmethod
     def weight_specs(cls, params: Dict[str, Any], prefix: str) -> List[WeightSpec]:
-        h, nh, d, vd, r, qr = (int(params[k]) for k in ("hidden", "heads", "dim", "vdim", "kv_rank", "q_rank"))
+        h, nh, d, vd, r = (int(params[k]) for k in ("hidden", "heads", "dim", "vdim", "kv_rank"))
+        qr, rot = int(params.get("q_rank") or 0), int(params.get("rot_dim") or 0)
         n = lambda leaf: cls.full_name(prefix, params, leaf)
+        if not qr:
+            return ([WeightSpec(n("q"), (nh * (d + rot), h), MATRIX), WeightSpec(n("dkv"), (r + rot, h), MATRIX),
+                     WeightSpec(n("dkv.norm"), (r,), VECTOR, init="one_plus_normal"), WeightSpec(n("uk"), (nh * d, r), MATRIX),
+                     WeightSpec(n("uv"), (nh * vd, r), MATRIX), WeightSpec(n("o"), (h, nh * vd), MATRIX)]
+                    + ([WeightSpec(n("sink"), (nh,), VECTOR, std=1.0)] if params.get("sink") else []))
         return [WeightSpec(n("dq"), (qr, h), MATRIX), WeightSpec(n("dq.norm"), (qr,), VECTOR, init="one_plus_normal"),
                 WeightSpec(n("uq"), (nh * d, qr), MATRIX),
                 WeightSpec(n("dkv"), (r, h), MATRIX), WeightSpec(n("dkv.norm"), (r,), VECTOR, init="one_plus_normal"),
@@ -103,10 +136,25 @@ class LatentAttention(Part):
 
     @classmethod
     def kv_need(cls, params: Dict[str, Any]) -> Optional[KVNeed]:
-        return KVNeed((CacheStream("latent", 1, int(params["kv_rank"])),), None)
+        return KVNeed((CacheStream("latent", 1, int(params["kv_rank"]) + int(params.get("rot_dim") or 0)),),
+                      int(params.get("window") or 0) or None)
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         n = lambda leaf: self.full_name(self.prefix, self.params, leaf)
+        if not self.q_rank:
+            mats = [tensors.pop(n(x)) for x in ("q", "dkv")]
+            if len({m.dtype for m in mats}) > 1:
+                mats = [m.float() for m in mats]
+            self.down = Linear(torch.cat(mats, dim=0))
+            del mats
+            self.wkv = tensors.pop(n("dkv.norm")).to(torch.float32).contiguous()
+            uk = tensors.pop(n("uk"))
+            self.uk_t = uk.view(self.heads, self.dim, self.kv_rank).transpose(1, 2).contiguous() if self.dim else None
+            self.uv = tensors.pop(n("uv")).view(self.heads, self.vdim, self.kv_rank).contiguous()
+            if self.has_sink:
+                self.sink = tensors.pop(n("sink")).to(torch.float32).contiguous()
+            self.o = Linear(tensors.pop(n("o")))
+            return
         mats = [tensors.pop(n(x)) for x in ("dq", "dkv", "g")]
         if len({m.dtype for m in mats}) > 1:
             mats = [m.float() for m in mats]
@@ -132,7 +180,7 @@ class LatentAttention(Part):
         of ``2 kv_rank`` multiplications per query, key and head.  Single
         tokens stay with the latents, which all their heads share."""
         dtype = weight_dtype if weight_dtype is not None else self.dtype
-        return (dtype == torch.bfloat16 and self.dtype == torch.bfloat16 and torch.device(self.device).type == "cuda"
+        return (self.plain and dtype == torch.bfloat16 and self.dtype == torch.bfloat16 and torch.device(self.device).type == "cuda"
                 and self.dim == self.vdim == ops.UMMA_ATTENTION_HEAD_DIM and self.kv_rank % 8 == 0)
 
     def describe_step(self, layout, put) -> LatentStep:
@@ -175,17 +223,19 @@ class LatentAttention(Part):
                 row_entry.append(i), row0.append(r0)
         return LatentStep(put(tile_entry), put(tile_q0), len(tile_entry), bm, put(row_entry), put(row0), len(row_entry), prompt)
 
-    def _per_head(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    def _per_head(self, x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """x ``[N, heads, a]`` (a view), w ``[heads, b, a]`` -> float32 ``[N, heads, b]``
-        (a view): head h's vectors times ``w[h]^T``."""
+        (a view, or ``out`` if given): head h's vectors times ``w[h]^T``."""
         n, width_out = x.shape[0], w.shape[1]
         if w.dtype == torch.float32:
-            out = torch.empty((n, self.heads, width_out), dtype=torch.float32, device=x.device)
+            if out is None:
+                out = torch.empty((n, self.heads, width_out), dtype=torch.float32, device=x.device)
             for h in range(self.heads):
                 ops.gemm_f32(x[:, h], w[h], None, out[:, h])
             return out
         # bfloat16 weights: one batched library product over the heads, float32 sums
-        return torch.bmm(x.transpose(0, 1), w.transpose(1, 2), out_dtype=torch.float32).transpose(0, 1)
+        y = torch.bmm(x.transpose(0, 1), w.transpose(1, 2), out_dtype=torch.float32).transpose(0, 1)
+        return y if out is None else out.copy_(y)
 
     def inner(self, x: torch.Tensor, ctx, run: RunInfo, position=None, out: torch.Tensor = None) -> torch.Tensor:
         """The gated heads ``[N, heads * vdim]`` that the output projection takes;
@@ -195,6 +245,8 @@ class LatentAttention(Part):
         g = run.kv_group
         views, page_stride = ctx.kv.stream_views(g, run.kv_index)
         cache = views["latent"]
+        if not self.plain:
+            return self._inner_options(x, ctx, position, out, step, g, cache, page_stride)
         p = self.down.forward(x, out_dtype=torch.float32)
         cq = torch.empty((n, self.q_rank), dtype=x.dtype, device=x.device)
         gate = torch.empty((n, self.heads), dtype=torch.float32, device=x.device)
@@ -225,6 +277,35 @@ class LatentAttention(Part):
             return ops.gate_heads(heads, gate, out, prompt.row_entry, ctx.entry_q_len, prompt_rows=False)
         return ops.gate_heads(heads, gate, out)
 
+    def _inner_options(self, x, ctx, position, out, step: LatentStep, g, cache, page_stride) -> torch.Tensor:
+        """The mixer with its options (a direct query projection, a rotated part, a window, a sink; no gates):
+        the kernel's queries are ``[Uk_h^T q_plain_h | q_rot_h]`` against cached rows ``[c | k_rot]``."""
+        n, nh, r, rot = x.shape[0], self.heads, self.kv_rank, self.rot_dim
+        if rot:
+            if not (isinstance(position, (tuple, list)) and len(position) == 2 and 2 * position[0].shape[1] == rot):
+                raise TypeError("latent_attention takes its position as a pair (cos, sin) of [N, rot_dim / 2] float32 tensors; "
+                                "the layer's position encoding gave something else")
+            cos, sin = position
+        else:
+            cos = sin = torch.empty((n, 0), dtype=torch.float32, device=x.device)
+        p = self.down.forward(x, out_dtype=torch.float32)                      # [q heads | latent | rotating key part]
+        q_plain = torch.empty((n, nh * self.dim), dtype=x.dtype, device=x.device)
+        q_rows = torch.empty((n, nh, self.width), dtype=torch.float32, device=x.device)
+        ops.latent_rope_prep(p, self.wkv, self.eps, nh, self.dim, rot, r, cos, sin, q_plain, q_rows, cache, page_stride,
+                             ctx.page_size, ctx.slot_maps[g])
+        if self.dim:
+            self._per_head(q_plain.view(n, nh, self.dim), self.uk_t, out=q_rows[:, :, :r])
+        else:
+            q_rows[:, :, :r].zero_()
+        o_lat = torch.empty((nh, n, r), dtype=x.dtype, device=x.device).transpose(0, 1)
+        ops.attn_latent_paged(q_rows, o_lat, cache, page_stride, ctx.page_size, ctx.block_tables[g], step.tile_entry,
+                              step.tile_q0, step.n_tiles, ctx.entry_q_start, ctx.entry_q_len, ctx.entry_ctx_start,
+                              self.scale, window=self.window, sink=self.sink)
+        heads = self._per_head(o_lat, self.uv)                                 # float32 [N, heads, vdim]
+        if out is None:
+            out = torch.empty((n, nh * self.vdim), dtype=x.dtype, device=x.device)
+        return ops.gate_heads(heads, None, out)
+
     def _attend_portions(self, q, gate, out, ctx, prompt: "PromptStep", cache, page_stride, g) -> None:
         """The step's prompt portions per head: expand the cached latents of
         their contexts into keys and values, laid out in pages of their own,
@@ -248,7 +329,7 @@ class LatentAttention(Part):
         return self.heads * self.vdim
 
     def forward(self, x: torch.Tensor, ctx, run: RunInfo, position) -> torch.Tensor:
-        return self.o.forward(self.inner(x, ctx, run), out_dtype=torch.float32)
+        return self.o.forward(self.inner(x, ctx, run, position), out_dtype=torch.float32)
 
 
 register_part("mixer", "latent_attention", LatentAttention)

@@ -15,7 +15,7 @@ import torch
 from ..config.registry import register_part
 from ..kernels import ops
 from ..weights.loader import VECTOR, WeightSpec
-from .base import BranchMean, NormedDelta, Part, PartialSums
+from .base import BranchMean, NormedDelta, Part, PartialSums, ScaledSum
 
 
 class RMSNorm(Part):
@@ -126,5 +126,39 @@ class LayerNorm(Part):
         return ops.add_layernorm(residual, delta, self.weight, self.eps, out, rows, n_partials, out32)
 
 
+class GroupRMSNorm(RMSNorm):
+    """RMS norm over ``groups`` equal consecutive parts of the row, each divided by its own root mean square, the whole
+    multiplied by one weight of the row's length; fused with the sum into the stream like :class:`RMSNorm`.
+    ``delta`` may also be a :class:`ScaledSum` of two branches: the weighted sum, the sum into the stream and the norm
+    are one kernel.  params: those of ``rmsnorm`` and ``groups`` (default 1, which is the plain norm)."""
+
+    family = "norm"
+
+    def __init__(self, params, prefix, dtype, device):
+        super().__init__(params, prefix, dtype, device)
+        self.groups = int(params.get("groups") or 1)
+        if self.groups < 1 or self.hidden % self.groups:
+            raise ValueError(f"group_rmsnorm: {self.groups} groups do not divide a row of {self.hidden}")
+
+    def forward(self, residual: torch.Tensor, delta, out: Optional[torch.Tensor] = None,
+                rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        n_rows = rows.numel() if rows is not None else residual.shape[0]
+        if out is None:
+            out = torch.empty((n_rows, self.hidden), dtype=self.dtype, device=residual.device)
+        if isinstance(delta, NormedDelta) or isinstance(delta, BranchMean):
+            raise TypeError("group_rmsnorm takes a tensor, partial sums or a weighted sum of two branches")
+        terms = delta.terms if isinstance(delta, ScaledSum) else ([(delta, 1.0)] if delta is not None else [])
+        if len(terms) > 2:
+            raise ValueError("a weighted sum is built for two branches")
+        flat = [((v.tensor if isinstance(v, PartialSums) else v), float(f)) for v, f in terms] + [(None, 1.0)] * (2 - len(terms))
+        (a, fa), (b, fb) = flat
+        if rows is not None and (a is not None or b is not None):
+            # picked rows leave the stream untouched: the pending sum goes in first
+            ops.add_group_rmsnorm(residual, a, self.weight, self.eps, self.groups, None, None, fa, b, fb)
+            a = b = None
+        return ops.add_group_rmsnorm(residual, a, self.weight, self.eps, self.groups, out, rows, fa, b, fb)
+
+
 register_part("norm", "rmsnorm", RMSNorm)
+register_part("norm", "group_rmsnorm", GroupRMSNorm)
 register_part("norm", "layernorm", LayerNorm)

@@ -19,6 +19,10 @@ decoder designs, each a parameter:
   ``sink``               one more term of score 0 and no value in the denominator:
                          p_j = exp(s_j) / (1 + sum exp(s_j))
   ``gate``               the heads' results times sigmoid(g), element by element, ahead of the output projection
+  ``bias``               q, k, v and the output projection have a bias each, added in the projection
+  ``q_temp``             {coef, every}: the query at position p is multiplied by 1 + coef * ln(floor((p + 1) / every) + 1)
+  ``distance_toll``      the score of key j for the query at p loses r1_h * ln(1 + r2_h * (p - j)), with two stored
+                         numbers per head (after the cap, if there is one)
 
 Keys are ``dim`` wide, values ``vdim``.  Keys (rotated) and values live in the paged cache; the last
 ``taps - 1`` projected rows of a sequence live in its state slot, so a prompt may be cut anywhere.  Scores,
@@ -83,7 +87,8 @@ class WindowAttention(Part):
     """params: ``hidden``, ``heads``, ``kv_heads``, ``dim``, ``vdim``, ``conv`` (taps, 0 = none), ``rot_dims``,
     ``rot_layout`` (``interleaved`` or ``half``), ``scale`` (None = ``dim^-1/2``), ``softcap`` (None = none),
     ``window`` (None = all keys), ``keep_first``, ``sink``, ``gate``, ``qk_norm``, ``v_norm``, ``v_mix`` (None,
-    ``first`` or ``blend``), ``eps`` (of these norms), ``name``.  Tensors ``<prefix>.<name>.{q,k,v,g,o}``,
+    ``first`` or ``blend``), ``eps`` (of these norms), ``bias``, ``q_temp``, ``distance_toll``, ``name``.  Tensors
+    ``<prefix>.<name>.{q,k,v,g,o}``, ``<prefix>.<name>.{q,k,v,o}.b``, ``<prefix>.<name>.{r1,r2}`` ``[heads]``,
     ``<prefix>.<name>.{q,k,v}.conv`` ``[channels, taps]``, ``<prefix>.<name>.{q,k}.norm`` and ``<prefix>.<name>.vmix``
     (one number; stored but unused in the ``first`` layer).
     State: ``conv_tail`` float32 ``[taps - 1, channels of q, k and v]``.
@@ -110,6 +115,13 @@ class WindowAttention(Part):
         self.sink, self.gate = bool(p.get("sink")), bool(p.get("gate"))
         self.qk_norm, self.v_norm, self.v_mix = bool(p.get("qk_norm")), bool(p.get("v_norm")), p.get("v_mix") or None
         self.eps = float(p.get("eps") or 0.0)
+        self.bias = bool(p.get("bias"))
+        qt = p.get("q_temp") or None
+        self.q_temp = (float(qt["coef"]), int(qt["every"])) if qt else None
+        if self.q_temp and self.q_temp[1] < 1:
+            raise ValueError("window_attention: q_temp.every must be at least 1")
+        self.distance_toll = bool(p.get("distance_toll"))
+        self.toll = None
         if self.v_mix not in (None, "first", "blend"):
             raise ValueError(f"v_mix {self.v_mix!r} is not one of None, 'first', 'blend'")
         self.normed = self.qk_norm or self.v_norm or self.v_mix is not None
@@ -151,6 +163,11 @@ class WindowAttention(Part):
         if params.get("v_mix"):
             specs.append(WeightSpec(n("vmix"), (), VECTOR, std=0.3))
         specs.append(WeightSpec(n("o"), (h, nh * vd), MATRIX))
+        if params.get("bias"):
+            specs += [WeightSpec(n(f"{x}.b"), (r,), VECTOR) for x, r in rows.items()] + [WeightSpec(n("o.b"), (h,), VECTOR)]
+        if params.get("distance_toll"):
+            specs += [WeightSpec(n("r1"), (nh,), VECTOR, init="abs_normal", std=0.5),
+                      WeightSpec(n("r2"), (nh,), VECTOR, init="abs_normal", std=0.5)]
         return specs
 
     @classmethod
@@ -170,8 +187,14 @@ class WindowAttention(Part):
         mats = [tensors.pop(n(x)) for x in names]
         if len({m.dtype for m in mats}) > 1:
             mats = [m.float() for m in mats]
-        self.qkvg = Linear(torch.cat(mats, dim=0))
+        bias = None
+        if self.bias:
+            bias = torch.cat([tensors.pop(n(f"{x}.b")).float() for x in ("q", "k", "v")]
+                             + ([torch.zeros(mats[3].shape[0], device=mats[3].device)] if self.gate else []))
+        self.qkvg = Linear(torch.cat(mats, dim=0), bias)
         del mats
+        if self.distance_toll:
+            self.toll = tuple(tensors.pop(n(x)).to(torch.float32).contiguous() for x in ("r1", "r2"))
         if self.taps >= 1:
             self.conv_w = torch.cat([tensors.pop(n(f"{x}.conv")).float() for x in ("q", "k", "v")]).contiguous()
         if self.qk_norm:
@@ -179,7 +202,7 @@ class WindowAttention(Part):
             self.k_norm_w = tensors.pop(n("k.norm")).to(torch.float32).contiguous()
         if self.v_mix:
             self.mix_lambda = tensors.pop(n("vmix")).to(torch.float32).reshape(1).contiguous()
-        self.o = Linear(tensors.pop(n("o")))
+        self.o = Linear(tensors.pop(n("o")), tensors.pop(n("o.b")) if self.bias else None)
 
     def describe_step(self, layout, put) -> QueryTiles:
         return describe_query_tiles(layout, put)
@@ -228,16 +251,17 @@ class WindowAttention(Part):
         common = (ctx.entry_q_start, ctx.entry_q_len, ctx.entry_ctx_start, self.heads, self.kv_heads, self.dim, self.scale,
                   self.window)
         rest = (self.vdim, self.softcap, self.keep_first, self.sink, gate)
+        more = dict(q_temp=self.q_temp, distance_toll=self.toll)
         pages = (k_layer, v_layer, page_stride, ctx.page_size, ctx.block_tables[g])
         if step.n_single:       # decoded tokens and the shortest portions: a block a token and head
             ops.attn_paged_options(q, q.stride(0), out, *pages, step.single_entry, step.single_q0, step.n_single, *common, *rest,
-                                   single_tokens=True)
+                                   single_tokens=True, **more)
         if step.n_chunk and (self.TENSOR_CORES and x.dtype == torch.bfloat16 and self.dim == self.vdim and out.is_contiguous()
-                             and self.dim in ops.FAST_ATTENTION_HEAD_DIMS):
+                             and self.dim in ops.FAST_ATTENTION_HEAD_DIMS and not self.q_temp and not self.toll):
             ops.attn_prefill_options_bf16(q, q.stride(0), out, *pages, step.chunk_entry, step.chunk_q0, step.n_chunk, *common,
                                           self.softcap, self.keep_first, self.sink, gate)      # portions on tensor cores
         elif step.n_tiles:
-            ops.attn_paged_options(q, q.stride(0), out, *pages, step.tile_entry, step.tile_q0, step.n_tiles, *common, *rest)
+            ops.attn_paged_options(q, q.stride(0), out, *pages, step.tile_entry, step.tile_q0, step.n_tiles, *common, *rest, **more)
         return out
 
     def forward(self, x: torch.Tensor, ctx, run: RunInfo, position):

@@ -34,7 +34,7 @@ class WeightSpec:
     files but is not loaded, e.g. an output head that is tied to the
     embedding).
     init: how the random-weights mode fills it: ``normal`` N(0, std) or
-    ``one_plus_normal`` 1 + N(0, std).
+    ``one_plus_normal`` 1 + N(0, std), ``abs_normal`` |N(0, std)| (numbers that must not be negative).
     A dimension given as -1 is one that no configuration key names: the stored
     tensor's own size stands (the part reads it at load); random weights take
     ``free_size`` there.

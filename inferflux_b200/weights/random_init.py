@@ -41,6 +41,8 @@ def random_tensors(specs: Iterable[WeightSpec], seed: int, dtype: torch.dtype = 
         t = torch.randn(shape, generator=gen, dtype=torch.float32, device=device) * s.std
         if s.init == "one_plus_normal":
             t += 1.0
+        elif s.init == "abs_normal":
+            t = t.abs()
         store = (vector_dtype or dtype) if s.kind == VECTOR else dtype
         out[s.name] = t.to(store)
     return out

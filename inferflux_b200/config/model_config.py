@@ -722,9 +722,7 @@ class MalazenConfig(ModelConfig):
 
     @staticmethod
     def _latent(m: Dict[str, Any], where: str) -> Dict[str, Any]:
-        dim, rot_dim = _require_int(m, "dim", 0), _require_int(m, "rot_dim", 0) if m.get("rot_dim") is not None else 0
-        if dim + rot_dim < 1:
-            raise ConfigError(f"{where}: dim + rot_dim must be positive")
+        dim, rot_dim = _require_int(m, "dim"), _require_int(m, "rot_dim", 0) if m.get("rot_dim") is not None else 0
         out = {"heads": _require_int(m, "heads"), "dim": dim, "rot_dim": rot_dim, "vdim": _require_int(m, "vdim"),
                "kv_rank": _require_int(m, "kv_rank"),
                "scale": _require_number(m, "scale", where) if m.get("scale") is not None else float(dim + rot_dim) ** -0.5,

@@ -149,7 +149,7 @@ class LatentAttention(Part):
             del mats
             self.wkv = tensors.pop(n("dkv.norm")).to(torch.float32).contiguous()
             uk = tensors.pop(n("uk"))
-            self.uk_t = uk.view(self.heads, self.dim, self.kv_rank).transpose(1, 2).contiguous() if self.dim else None
+            self.uk_t = uk.view(self.heads, self.dim, self.kv_rank).transpose(1, 2).contiguous()
             self.uv = tensors.pop(n("uv")).view(self.heads, self.vdim, self.kv_rank).contiguous()
             if self.has_sink:
                 self.sink = tensors.pop(n("sink")).to(torch.float32).contiguous()
@@ -293,10 +293,7 @@ class LatentAttention(Part):
         q_rows = torch.empty((n, nh, self.width), dtype=torch.float32, device=x.device)
         ops.latent_rope_prep(p, self.wkv, self.eps, nh, self.dim, rot, r, cos, sin, q_plain, q_rows, cache, page_stride,
                              ctx.page_size, ctx.slot_maps[g])
-        if self.dim:
-            self._per_head(q_plain.view(n, nh, self.dim), self.uk_t, out=q_rows[:, :, :r])
-        else:
-            q_rows[:, :, :r].zero_()
+        self._per_head(q_plain.view(n, nh, self.dim), self.uk_t, out=q_rows[:, :, :r])
         o_lat = torch.empty((nh, n, r), dtype=x.dtype, device=x.device).transpose(0, 1)
         ops.attn_latent_paged(q_rows, o_lat, cache, page_stride, ctx.page_size, ctx.block_tables[g], step.tile_entry,
                               step.tile_q0, step.n_tiles, ctx.entry_q_start, ctx.entry_q_len, ctx.entry_ctx_start,

@@ -355,3 +355,94 @@ def make_tekosun_folder(cfg: dict, seed: int, folder: Optional[str] = None, **kw
         json.dump(cfg, f)
     write_safetensors(os.path.join(folder, "model.safetensors"), tensors)
     return folder
+
+
+# ------------------------------------------------------------------ Malazen
+def _ml_left(heads, dim, kv_heads=None, vdim=None, scale=None, q_temp=None):
+    m = dict(heads=heads, dim=dim)
+    for k, v in (("kv_heads", kv_heads), ("vdim", vdim), ("scale", scale), ("q_temp", q_temp)):
+        if v is not None:
+            m[k] = v
+    return m
+
+
+def _ml_parallel(left, right, mlp=None, left_scale=None, right_scale=None):
+    mixer = dict(left=left, right=right)
+    if left_scale is not None:
+        mixer.update(left_scale=left_scale, right_scale=right_scale)
+    return dict(type="parallel", mixer=mixer, mlp=mlp)
+
+
+def _ml_latent(heads, dim, vdim, kv_rank, rot_dim=None, mask=None, rot=None, scale=None, mlp=None):
+    m = dict(heads=heads, dim=dim, vdim=vdim, kv_rank=kv_rank)
+    for k, v in (("rot_dim", rot_dim), ("mask", mask), ("rot", rot), ("scale", scale)):
+        if v is not None:
+            m[k] = v
+    return dict(type="latent_attention", mixer=m, mlp=mlp)
+
+
+_ML_FF = lambda ff, limit: dict(kind="dense", ff=ff, limit=limit)
+# Tiny Malazen configurations that differ in every size, option and order of layers.  A: four norm groups; key, value
+# and decay sizes all different; a rotated part longer than the plain one with stretched frequencies; a window of 20; a
+# loop from layer 0 that runs three times; a layer without feed-forward.
+ML_A = dict(architecture="Malazen", width=64, vocab=300, norm=dict(eps=1e-5, groups=4), layers=[
+    _ml_parallel(_ml_left(4, 16, kv_heads=2, vdim=24, scale=0.3, q_temp=dict(coef=0.7, every=8)), dict(heads=3, dim=12, vdim=20, tau=4.0),
+                 _ML_FF(96, 2.0), 0.8, 1.3),
+    _ml_latent(3, 8, 20, 24, rot_dim=12, mask=dict(size=20), rot=dict(dims=12, base=1000.0, scaling=_YARN), scale=0.4, mlp=_ML_FF(72, 1.0)),
+    _ml_parallel(_ml_left(2, 32, kv_heads=1, scale=0.2, q_temp=dict(coef=0.25, every=30)), dict(heads=1, dim=16, vdim=8, tau=9.0), None, 1.5, 0.5)],
+    loop=dict(start=0, stop=2, times=3))
+# B: sizes that are no multiple of 4 or 8 anywhere, one norm group, a window shorter than a page, a latent layer without
+# rotated part and without window, a temperature that steps at every token and none at all, as many key/value heads
+# as heads, factors left out, no loop
+ML_B = dict(architecture="Malazen", width=50, vocab=77, norm=dict(eps=3e-6), layers=[
+    _ml_latent(2, 10, 7, 9, rot_dim=6, mask=dict(size=7), rot=dict(dims=6, base=50.0), scale=0.9, mlp=_ML_FF(35, 0.7)),
+    _ml_parallel(_ml_left(3, 10, vdim=6, q_temp=dict(coef=1.5, every=1)), dict(heads=2, dim=6, vdim=10, tau=1.0), _ML_FF(45, 3.0)),
+    _ml_latent(5, 6, 10, 13, mlp=None),
+    _ml_parallel(_ml_left(5, 6, kv_heads=1, vdim=10, scale=0.5), dict(heads=5, dim=10, tau=30.0), _ML_FF(18, 1.2), 1.0, 2.0)])
+# C: heads of 64 (the size tensor-core kernels take), a latent row of 64, windows longer than several pages, eight norm
+# groups, a loop over a single layer, a loop that ends with the last layer
+ML_C = dict(architecture="Malazen", width=128, vocab=200, norm=dict(eps=1e-6, groups=8), layers=[
+    _ml_latent(4, 32, 32, 48, rot_dim=16, mask=dict(size=70), rot=dict(dims=16, base=200000.0, scaling=_YARN), scale=0.15, mlp=_ML_FF(160, 1.5)),
+    _ml_parallel(_ml_left(4, 64, kv_heads=2, vdim=64, scale=0.125, q_temp=dict(coef=0.5, every=16)), dict(heads=2, dim=64, vdim=64, tau=12.0),
+                 _ML_FF(96, 2.5), 1.1, 0.7),
+    _ml_latent(2, 64, 64, 120, rot_dim=8, mask=dict(size=100), rot=dict(dims=8, base=1e4), scale=0.1, mlp=_ML_FF(64, 1.0))],
+    loop=dict(start=2, stop=3, times=2))
+ML = {"A": ML_A, "B": ML_B, "C": ML_C}
+
+
+def malazen_tensors(cfg: dict, seed: int, sharpen: float = 8.0):
+    """Random tensors (bfloat16 matrices) for a Malazen configuration.  ``sharpen`` multiplies the attentions' query
+    and key projections so that the softmax is peaked on single keys wherever they lie (with N(0, 0.02) weights it is
+    nearly uniform, and a lost key among hundreds or a missing sink would hide below the bfloat16 tolerance); the
+    other projections are enlarged so that every branch carries weight in the sums, and the decays' biases are raised
+    so that a state lost many tokens back would show."""
+    from inferflux_b200.config import load_config
+    from inferflux_b200.config.registry import build_spec
+    from inferflux_b200.engine.model import Model
+    from inferflux_b200.weights.random_init import random_tensors
+    config = load_config(json.loads(json.dumps(cfg)))
+    specs = Model(build_spec(config), torch.float32, "cpu").weight_specs()
+    tensors = random_tensors(specs, seed, torch.bfloat16, None, "cpu")
+    for name in tensors:
+        f, add = 1.0, 0.0
+        if name.endswith((".left.q", ".left.k", ".mix.q", ".mix.uk", ".mix.dkv")):
+            f = sharpen
+        elif name.endswith((".right.q", ".right.k", ".right.v", ".left.v", ".g", ".o", ".up", ".down", ".gate", ".uv", ".a1")):
+            f = 4.0
+        elif name.endswith(".a2.b"):
+            add = 2.0
+        elif name == "embed":
+            f = 20.0
+        if f != 1.0 or add:
+            tensors[name] = (tensors[name].float() * f + add).to(tensors[name].dtype)
+    return config, tensors
+
+
+def make_malazen_folder(cfg: dict, seed: int, folder: Optional[str] = None, **kw) -> str:
+    from inferflux_b200.weights.safetensors_io import write_safetensors
+    folder = folder or tempfile.mkdtemp(prefix="ifx_ml_")
+    config, tensors = malazen_tensors(cfg, seed, **kw)
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    write_safetensors(os.path.join(folder, "model.safetensors"), tensors)
+    return folder

@@ -12,6 +12,13 @@ import math
 import torch
 
 F64 = torch.float64
+#: None, or a type to which every matrix product's input and result, what is cached and what is activated are
+#: rounded: that run is the model of what rounding alone does to the logits.
+ROUND = [None]
+
+
+def _r(v):
+    return v if ROUND[0] is None else v.to(ROUND[0]).to(F64)
 
 
 def group_norm(v, weight, eps, groups):
@@ -25,8 +32,8 @@ def group_norm(v, weight, eps, groups):
 
 def linear(v, w, name):
     """``W v`` plus the bias ``<name>.b`` if the model has one."""
-    y = v @ w[name].T
-    return y + w[name + ".b"] if name + ".b" in w else y
+    y = _r(v) @ w[name].T
+    return _r(y + w[name + ".b"] if name + ".b" in w else y)
 
 
 def query_temperature(positions, coef, every):
@@ -38,9 +45,12 @@ def biased_attention(h, w, name, m, positions=None):
     """Grouped-query attention over every earlier position without rotation: the query grows with its position,
     and a score loses ``r1_h * ln(1 + r2_h * distance)``."""
     t = h.shape[0]
-    nh, nkv, d, vd = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    nh, d = m["heads"], m["dim"]
+    nkv, vd, scale = m.get("kv_heads") or nh, m.get("vdim") or d, m.get("scale") or d ** -0.5
     pos = torch.arange(t) if positions is None else positions
-    q = linear(h, w, name + ".q").reshape(t, nh, d) * query_temperature(pos, m["q_temp"]["coef"], m["q_temp"]["every"])[:, None, None]
+    q = linear(h, w, name + ".q").reshape(t, nh, d)
+    if m.get("q_temp"):
+        q = q * query_temperature(pos, m["q_temp"]["coef"], m["q_temp"]["every"])[:, None, None]
     k = linear(h, w, name + ".k").reshape(t, nkv, d)
     v = linear(h, w, name + ".v").reshape(t, nkv, vd)
     dist = (pos[:, None] - pos[None, :]).to(F64)
@@ -48,7 +58,7 @@ def biased_attention(h, w, name, m, positions=None):
     out = torch.zeros((t, nh, vd), dtype=F64)
     for head in range(nh):
         kv = head // (nh // nkv)
-        s = (q[:, head] @ k[:, kv].T) * m["scale"]
+        s = (q[:, head] @ k[:, kv].T) * scale
         s = s - w[name + ".r1"][head] * torch.log(1.0 + w[name + ".r2"][head] * dist.clamp(min=0.0))
         s = s.masked_fill(~seen, -math.inf)
         out[:, head] = torch.softmax(s, dim=-1) @ v[:, kv]
@@ -57,7 +67,7 @@ def biased_attention(h, w, name, m, positions=None):
 
 def channel_decay(h, w, name, m):
     """alpha = sigmoid(z)^(1 / tau), z = W_a2 (W_a1 h) + b: one number per head and key channel."""
-    z = (h @ w[name + ".a1"].T) @ w[name + ".a2"].T + w[name + ".a2.b"]
+    z = linear(h, w, name + ".a1") @ w[name + ".a2"].T + w[name + ".a2.b"]
     return torch.exp(torch.nn.functional.logsigmoid(z) / m["tau"])
 
 
@@ -66,10 +76,11 @@ def gated_linear_attention(h, w, name, m, eps, state=None):
     by its root mean square and multiplied by ``.norm``; heads side by side times silu(W_g h); W_o.
     Returns (result, the state after the last token)."""
     t = h.shape[0]
-    nh, d, vd = m["heads"], m["dim"], m["vdim"]
-    q = (h @ w[name + ".q"].T).reshape(t, nh, d) * d ** -0.5
-    k = (h @ w[name + ".k"].T).reshape(t, nh, d)
-    v = (h @ w[name + ".v"].T).reshape(t, nh, vd)
+    nh, d = m["heads"], m["dim"]
+    vd = m.get("vdim") or d
+    q = linear(h, w, name + ".q").reshape(t, nh, d) * d ** -0.5
+    k = linear(h, w, name + ".k").reshape(t, nh, d)
+    v = linear(h, w, name + ".v").reshape(t, nh, vd)
     alpha = channel_decay(h, w, name, m).reshape(t, nh, d)
     s = torch.zeros((nh, d, vd), dtype=F64) if state is None else state.clone()
     o = torch.zeros((t, nh, vd), dtype=F64)
@@ -77,14 +88,14 @@ def gated_linear_attention(h, w, name, m, eps, state=None):
         s = alpha[i][:, :, None] * s + k[i][:, :, None] * v[i][:, None, :]
         o[i] = torch.einsum("hdv,hd->hv", s, q[i])
     o = o / torch.sqrt((o * o).mean(-1, keepdim=True) + eps) * w[name + ".norm"]
-    g = h @ w[name + ".g"].T
-    return (o.reshape(t, nh * vd) * g * torch.sigmoid(g)) @ w[name + ".o"].T, s
+    g = linear(h, w, name + ".g")
+    return linear(o.reshape(t, nh * vd) * g * torch.sigmoid(g), w, name + ".o"), s
 
 
 def parallel_mixer(h, w, name, m, eps, state=None):
     left = biased_attention(h, w, name + ".left", m["left"])
     right, state = gated_linear_attention(h, w, name + ".right", m["right"], eps, state)
-    return m["left_scale"] * left + m["right_scale"] * right, state
+    return m.get("left_scale", 1.0) * left + m.get("right_scale", 1.0) * right, state
 
 
 def rotary_frequencies(rot):
@@ -117,26 +128,27 @@ def latent_attention(h, w, name, m, eps, positions=None):
     """Keys and values of every head from one normed latent per token; one rotated key part for all heads; a
     window; a sink in the softmax's denominator."""
     t = h.shape[0]
-    nh, d, rd, vd, r = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+    nh, d, rd, vd, r = m["heads"], m["dim"], m.get("rot_dim") or 0, m["vdim"], m["kv_rank"]
+    scale = m.get("scale") or (d + rd) ** -0.5
     pos = torch.arange(t) if positions is None else positions
-    q = (h @ w[name + ".q"].T).reshape(t, nh, d + rd)
-    q_plain, q_rot = q[..., :d], rotate_pairs(q[..., d:], pos, m["rot"])
-    down = h @ w[name + ".dkv"].T
+    q = linear(h, w, name + ".q").reshape(t, nh, d + rd)
+    q_plain, q_rot = q[..., :d], (rotate_pairs(q[..., d:], pos, m["rot"]) if rd else q[..., d:])
+    down = linear(h, w, name + ".dkv")
     c = down[:, :r]
-    c = c / torch.sqrt((c * c).mean(-1, keepdim=True) + eps) * w[name + ".dkv.norm"]
-    k_rot = rotate_pairs(down[:, r:], pos, m["rot"])
-    k_plain = (c @ w[name + ".uk"].T).reshape(t, nh, d)
-    v = (c @ w[name + ".uv"].T).reshape(t, nh, vd)
+    c = _r(c / torch.sqrt((c * c).mean(-1, keepdim=True) + eps) * w[name + ".dkv.norm"])
+    k_rot = _r(rotate_pairs(down[:, r:], pos, m["rot"])) if rd else down[:, r:]
+    k_plain = linear(c, w, name + ".uk").reshape(t, nh, d)
+    v = linear(c, w, name + ".uv").reshape(t, nh, vd)
     dist = pos[:, None] - pos[None, :]
     seen = (dist >= 0) & (dist < m["mask"]["size"]) if m.get("mask") else dist >= 0
     out = torch.zeros((t, nh, vd), dtype=F64)
     for head in range(nh):
-        s = (q_plain[:, head] @ k_plain[:, head].T + q_rot[:, head] @ k_rot.T) * m["scale"]
+        s = (q_plain[:, head] @ k_plain[:, head].T + q_rot[:, head] @ k_rot.T) * scale
         s = s.masked_fill(~seen, -math.inf)
         top = torch.maximum(s.max(-1, keepdim=True).values, w[name + ".sink"][head])
         e = torch.exp(s - top)
         out[:, head] = (e / (e.sum(-1, keepdim=True) + torch.exp(w[name + ".sink"][head] - top))) @ v[:, head]
-    return out.reshape(t, nh * vd) @ w[name + ".o"].T
+    return linear(out.reshape(t, nh * vd), w, name + ".o")
 
 
 def clamped_glu(h, w, name, limit):
@@ -159,7 +171,7 @@ def schedule(cfg):
 
 def forward(cfg, w, tokens, collect=None):
     """Logits ``[T, vocab]`` of a whole sequence.  ``collect`` (a list) takes the stream after every layer run."""
-    eps, groups = cfg["norm"]["eps"], cfg["norm"]["groups"]
+    eps, groups = cfg["norm"]["eps"], cfg["norm"].get("groups") or 1
     x0 = w["embed"][torch.as_tensor(tokens)]
     x = x0.clone()
     loop = cfg.get("loop")
@@ -179,4 +191,4 @@ def forward(cfg, w, tokens, collect=None):
             x = x + clamped_glu(group_norm(x, w[name + ".norm2"], eps, groups), w, name + ".mlp", spec["mlp"]["limit"])
         if collect is not None:
             collect.append(x.clone())
-    return group_norm(x, w["final.norm"], eps, groups) @ w["embed"].T
+    return _r(group_norm(x, w["final.norm"], eps, groups)) @ w["embed"].T

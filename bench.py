@@ -222,10 +222,28 @@ def tekosun_config(size: str, layers: int):
                 layers=[turn[i % 4] for i in range(layers)])
 
 
+def malazen_config(size: str, layers: int):
+    """A Malazen config.json at the widths of one of the family sizes above: layers in turn a pair of mixers side by side
+    (attention with the family's heads and kv heads of 128, biases, a query temperature and a toll on distance, beside
+    gated linear attention with half as many heads of 128 x 128 and a decay projection through 16) and latent attention
+    (the family's heads of 128 plain and 64 rotated dimensions over latents of 512, values of 128, a window of 1,024,
+    stretched frequencies, a sink per head); every layer with a clamped gated feed-forward of the family's width; the
+    norms taken in four groups; no loop."""
+    _, hidden, heads, kv_heads, inter, vocab, _ = SIZES[size]
+    left = dict(heads=heads, kv_heads=kv_heads, dim=128, vdim=128, scale=128 ** -0.5, q_temp=dict(coef=0.1, every=1024))
+    right = dict(heads=max(1, heads // 2), dim=128, vdim=128, tau=16.0)
+    pair = dict(type="parallel", mixer=dict(left=left, right=right, left_scale=1.0, right_scale=1.0), mlp=dict(kind="dense", ff=inter, limit=7.0))
+    latent = dict(type="latent_attention", mlp=dict(kind="dense", ff=inter, limit=7.0), mixer=dict(
+        heads=heads, dim=128, rot_dim=64, vdim=128, kv_rank=512, scale=192 ** -0.5, mask=dict(size=1024),
+        rot=dict(dims=64, base=500000.0, scaling=dict(factor=4.0, original=8192, fast=16.0, slow=2.0))))
+    return dict(architecture="Malazen", width=hidden, vocab=vocab, norm=dict(eps=1e-6, groups=4),
+                layers=[pair if i % 2 == 0 else latent for i in range(layers)])
+
+
 def architecture_workload(args) -> int:
-    """--arch kunonex / pemorax / tekosun: prefill (one 2,048-token prompt) and decode (batch 8 at the given context)
+    """--arch kunonex / pemorax / tekosun / malazen: prefill (one 2,048-token prompt) and decode (batch 8 at the given context)
     of a model of that design beside a model of the same width, layer count and vocabulary (Qwen2 with the same
-    feed-forward width; for tekosun the closest design, Pemorax), both with random bfloat16 weights, device-timed
+    feed-forward width; for tekosun and malazen the closest design, Pemorax), both with random bfloat16 weights, device-timed
     with CUDA events after warm-up.  One JSON line."""
     import torch
     from inferflux_b200 import Engine, SamplingParams, StepEntry
@@ -234,9 +252,9 @@ def architecture_workload(args) -> int:
     warmup = max(3, args.warmup)
     greedy = SamplingParams(temperature=0.0, max_tokens=1 << 30, ignore_eos=True)
     arch = args.arch
-    design = {"kunonex": kunonex_config, "pemorax": pemorax_config, "tekosun": tekosun_config}[arch]
-    beside = "pemorax" if arch == "tekosun" else "qwen2"
-    beside_cfg = pemorax_config(args.size, layers) if arch == "tekosun" else dict(family_config(args.size), num_hidden_layers=layers)
+    design = {"kunonex": kunonex_config, "pemorax": pemorax_config, "tekosun": tekosun_config, "malazen": malazen_config}[arch]
+    beside = "pemorax" if arch in ("tekosun", "malazen") else "qwen2"
+    beside_cfg = pemorax_config(args.size, layers) if beside == "pemorax" else dict(family_config(args.size), num_hidden_layers=layers)
     out = {"metric": f"prefill and decode tokens/s, {arch.capitalize()} beside {beside.capitalize()} at the {args.size.upper()} widths", "impl": "ours",
            "n_gpus": 1, "dtype": "bf16", "data": "synthetic: seeded random weights, uniform random token ids",
            "steps": args.steps, "warmup": warmup,
@@ -309,12 +327,12 @@ def main() -> int:
     ap.add_argument("--mixed", type=int, default=0, metavar="N",
                     help="instead of the decode step: N requests with prompts of 128 to 2,048 tokens and 256 output "
                          "tokens each through Engine.generate (chunked prompts beside decoding requests)")
-    ap.add_argument("--arch", default="qwen2", choices=["qwen2", "kunonex", "pemorax", "tekosun"],
-                    help="kunonex, pemorax or tekosun: instead of the default workload, a model of that design beside a model "
-                         "of equal size (Qwen2; for tekosun, Pemorax) (--size, --layers, default 8), prefill and decode")
+    ap.add_argument("--arch", default="qwen2", choices=["qwen2", "kunonex", "pemorax", "tekosun", "malazen"],
+                    help="kunonex, pemorax, tekosun or malazen: instead of the default workload, a model of that design beside a "
+                         "model of equal size (Qwen2; for tekosun and malazen, Pemorax) (--size, --layers, default 8), prefill and decode")
     args = ap.parse_args()
 
-    if args.arch in ("kunonex", "pemorax", "tekosun") and args.impl == "ours":
+    if args.arch in ("kunonex", "pemorax", "tekosun", "malazen") and args.impl == "ours":
         return architecture_workload(args)
     if args.impl == "reference":
         return reference_arm()

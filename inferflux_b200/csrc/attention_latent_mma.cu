@@ -16,6 +16,12 @@
 //
 // Scores, maxima, sums and O are float32; Q and P enter the products rounded to bfloat16, C is bfloat16 as
 // cached.  Causal: key j is visible to a row whose token is at position p iff j <= p.
+//
+// Options: a cached row may be wider than the latent (R columns, of which the first `vrank` are the latent that
+// serves as value; the rest, a rotated key part that all heads share, enters the scores only: O is formed over
+// all R columns and the first vrank are written).  window > 0 hides keys j <= p - window, and the tiles wholly
+// behind the window of a tile's first row are never read.  sink ([n_heads] or null): one more term exp(sink[h])
+// without a value in the denominator, added once, at the end (by the merge kernel when the keys are split).
 #include "common.cuh"
 
 namespace {
@@ -65,7 +71,8 @@ __global__ void __launch_bounds__(256)
 attn_latent_mma_kernel(const float* __restrict__ q, HeadLayout ql, bf16* __restrict__ out, HeadLayout ol,
                        const bf16* __restrict__ cache, long long page_stride, int page_size, int page_shift,
                        LatentTiles b, int n_heads, int rank, float scale, int n_splits,
-                       float* __restrict__ part_o, float* __restrict__ part_ml) {
+                       float* __restrict__ part_o, float* __restrict__ part_ml, int vrank, int window,
+                       const float* __restrict__ sink) {
   constexpr bool BY_R = MT <= 2 && RT >= 2;
   constexpr int BN = NARROW ? 32 : 64;
   constexpr int BM = 16 * MT, RP = 64 * RT, LD = RP + PAD, LDP = BN + PAD, LDS = BN + 4;
@@ -96,8 +103,9 @@ attn_latent_mma_kernel(const float* __restrict__ q, HeadLayout ql, bf16* __restr
   const int last_tok = (row0 + n_rows - 1) / n_heads;
   const int kend = pos0 + last_tok;                                 // last key any row of the tile may see
   const int key_tiles = kend / BN + 1;
-  const int per = (key_tiles + n_splits - 1) / n_splits;
-  const int kt_lo = split * per, kt_hi = min(key_tiles, kt_lo + per);
+  const int kt_first = window > 0 ? max(0, pos0 + row0 / n_heads - window + 1) / BN : 0;     // tiles before it lie behind every row's window
+  const int per = (key_tiles - kt_first + n_splits - 1) / n_splits;
+  const int kt_lo = kt_first + split * per, kt_hi = min(key_tiles, kt_lo + per);
 
   // zero the padding columns once (no copy ever touches them), load Q as bfloat16
   for (int idx = tid; idx < (BM + 2 * BN) * (LD - rank); idx += blockDim.x) {
@@ -216,7 +224,8 @@ attn_latent_mma_kernel(const float* __restrict__ q, HeadLayout ql, bf16* __restr
       const int p = row_pos[r];                                      // -1 hides every key from a row that does not exist
       constexpr int KPL = BN / 32;                                   // keys a lane
       const int key = kt * BN + KPL * lane;
-      const bool v0 = key <= p, v1 = KPL > 1 && key + 1 <= p;
+      const bool v0 = key <= p && (window <= 0 || key > p - window);
+      const bool v1 = KPL > 1 && key + 1 <= p && (window <= 0 || key + 1 > p - window);
       float sc0, sc1 = 0.0f;
       if constexpr (KPL == 2) {
         float2 sc = *reinterpret_cast<const float2*>(ss + r * LDS + 2 * lane);
@@ -300,13 +309,18 @@ attn_latent_mma_kernel(const float* __restrict__ q, HeadLayout ql, bf16* __restr
       if (r >= n_rows) continue;
       const int rr = row0 + r, t = rr / n_heads, h = rr - t * n_heads;
       if (n_splits == 1) {
-        const float l = row_l[r];
-        const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+        float l = row_l[r], keep = 1.0f;
+        if (sink) {                // the sink joins the denominator: everything is brought to the larger maximum
+          const float mx = fmaxf(row_m[r], sink[h]);
+          keep = expf(row_m[r] - mx);
+          l = l * keep + expf(sink[h] - mx);
+        }
+        const float inv = l > 0.0f ? keep / l : 0.0f;
         bf16* orow = out + (size_t)(tok0 + t) * ol.row + (size_t)h * ol.head;
 #pragma unroll
         for (int n = 0; n < RT; ++n) {
           const int col = (warp * RT + n) * 8 + 2 * tq;
-          if (col < rank)          // rank is a multiple of 8: col + 1 < rank too
+          if (col < vrank)         // vrank is a multiple of 8: col + 1 < vrank too
             *reinterpret_cast<__nv_bfloat162*>(orow + col) = __floats2bfloat162_rn(o[m][n][2 * half] * inv, o[m][n][2 * half + 1] * inv);
         }
       } else {
@@ -331,7 +345,7 @@ attn_latent_mma_kernel(const float* __restrict__ q, HeadLayout ql, bf16* __restr
 // (its share of the common sum) is worked out once per row; the sums of the splits are then read side by side.
 __global__ void attn_latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          bf16* __restrict__ out, HeadLayout ol, LatentTiles b, int n_heads, int rank,
-                                         int n_splits, int bm) {
+                                         int n_splits, int bm, int vrank, const float* __restrict__ sink) {
   pdl_enter();
   __shared__ float w[64];
   const int tile = blockIdx.x, r = blockIdx.y;
@@ -345,16 +359,16 @@ __global__ void attn_latent_merge_kernel(const float* __restrict__ part_o, const
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
     if (lane < n_splits) { m0 = part_ml[(first + (size_t)lane * bm) * 2]; l0 = part_ml[(first + (size_t)lane * bm) * 2 + 1]; }
     if (lane + 32 < n_splits) { m1 = part_ml[(first + (size_t)(lane + 32) * bm) * 2]; l1 = part_ml[(first + (size_t)(lane + 32) * bm) * 2 + 1]; }
-    const float mx = warp_max(fmaxf(m0, m1));
+    const float mx = fmaxf(warp_max(fmaxf(m0, m1)), sink ? sink[h] : -INFINITY);
     const float e0 = m0 == -INFINITY ? 0.0f : expf(m0 - mx), e1 = m1 == -INFINITY ? 0.0f : expf(m1 - mx);
-    const float l = warp_sum(l0 * e0 + l1 * e1);
+    const float l = warp_sum(l0 * e0 + l1 * e1) + (sink ? expf(sink[h] - mx) : 0.0f);
     const float inv = l > 0.0f ? 1.0f / l : 0.0f;
     w[lane] = e0 * inv;
     w[lane + 32] = e1 * inv;
   }
   __syncthreads();
   bf16* orow = out + (size_t)(b.entry_q_start[e] + t) * ol.row + (size_t)h * ol.head;
-  for (int d = threadIdx.x; d < rank; d += blockDim.x) {
+  for (int d = threadIdx.x; d < vrank; d += blockDim.x) {
     const float* p = part_o + first * rank + d;
     float acc = 0.0f;
     int s = 0;
@@ -378,7 +392,7 @@ size_t smem_bytes() {
 template <int MT, int RT, bool NARROW>
 int launch_mma(const float* q, HeadLayout ql, bf16* out, HeadLayout ol, const bf16* cache, long long page_stride,
                int page_size, LatentTiles b, int n_tiles, int n_heads, int rank, float scale, int n_splits,
-               float* part_o, float* part_ml, cudaStream_t stream) {
+               float* part_o, float* part_ml, int vrank, int window, const float* sink, cudaStream_t stream) {
   const size_t smem = smem_bytes<MT, RT, NARROW>();
   auto kern = attn_latent_mma_kernel<MT, RT, NARROW>;
   if (smem > 48 * 1024) {
@@ -388,11 +402,11 @@ int launch_mma(const float* q, HeadLayout ql, bf16* out, HeadLayout ol, const bf
   int page_shift = 0;
   while ((1 << page_shift) < page_size) ++page_shift;
   int rc = launch_pdl(kern, dim3(n_tiles, n_splits), dim3(256), smem, stream, q, ql, out, ol, cache, page_stride, page_size,
-                      page_shift, b, n_heads, rank, scale, n_splits, part_o, part_ml);
+                      page_shift, b, n_heads, rank, scale, n_splits, part_o, part_ml, vrank, window, sink);
   if (rc) return rc;
   if (n_splits > 1) {
     rc = launch_pdl(attn_latent_merge_kernel, dim3(n_tiles, 16 * MT), dim3(rank > 256 ? 256 : (rank > 64 ? 128 : 64)), 0, stream,
-                    (const float*)part_o, (const float*)part_ml, out, ol, b, n_heads, rank, n_splits, 16 * MT);
+                    (const float*)part_o, (const float*)part_ml, out, ol, b, n_heads, rank, n_splits, 16 * MT, vrank, sink);
     if (rc) return rc;
   }
   return IFX_LAUNCH_CHECK();
@@ -426,14 +440,18 @@ IFX_API int ifx_attn_latent_mma_plan(int n_tiles, int bm, int rank, int max_keys
 // q float32 and out bfloat16 hold a (token, head) vector at token * row + head * head elements.  Tiles: bm (16 or
 // 64) consecutive (token, head) rows of one entry, listed by tile_entry / tile_row0.  n_splits > 1: part_o holds
 // n_tiles * n_splits * bm * rank floats, part_ml n_tiles * n_splits * bm * 2.
-IFX_API int ifx_attn_latent_mma(const float* q, long long q_row, long long q_head, void* out, long long o_row,
-                                long long o_head, const void* cache, long long page_stride, int page_size,
-                                const int* block_tables, int bt_stride, const int* tile_entry, const int* tile_row0,
-                                int n_tiles, int bm, const int* entry_q_start, const int* entry_q_len,
-                                const int* entry_ctx_start, int n_heads, int rank, float scale, int n_splits,
-                                float* part_o, float* part_ml, cudaStream_t stream) {
+// vrank (a multiple of 8, at most rank): the first columns of a cached row that are the latent and are written to
+// out; window: 0 = none; sink: float32 [n_heads] or null.
+IFX_API int ifx_attn_latent_mma_ex(const float* q, long long q_row, long long q_head, void* out, long long o_row,
+                                   long long o_head, const void* cache, long long page_stride, int page_size,
+                                   const int* block_tables, int bt_stride, const int* tile_entry, const int* tile_row0,
+                                   int n_tiles, int bm, const int* entry_q_start, const int* entry_q_len,
+                                   const int* entry_ctx_start, int n_heads, int rank, float scale, int n_splits,
+                                   float* part_o, float* part_ml, int vrank, int window, const float* sink,
+                                   cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (rank < 8 || rank > 512 || rank % 8 || n_heads < 1 || n_splits < 1 || n_splits > 64) return IFX_ERR_UNSUPPORTED;
+  if (vrank < 8 || vrank > rank || vrank % 8 || window < 0) return IFX_ERR_UNSUPPORTED;
   if (page_size <= 0 || (page_size & (page_size - 1)) || (page_stride & 7)) return IFX_ERR_UNSUPPORTED;
   if (((uintptr_t)cache & 15) != 0) return IFX_ERR_ALIGNMENT;
   if (n_splits > 1 && (!part_o || !part_ml)) return IFX_ERR_UNSUPPORTED;
@@ -441,10 +459,10 @@ IFX_API int ifx_attn_latent_mma(const float* q, long long q_row, long long q_hea
   HeadLayout ql{q_row, q_head}, ol{o_row, o_head};
   const int rt = (rank + 63) / 64;
 #define IFX_LM(MT, RT) return launch_mma<MT, RT, false>(q, ql, (bf16*)out, ol, (const bf16*)cache, page_stride, page_size, b, n_tiles, \
-                                                 n_heads, rank, scale, n_splits, part_o, part_ml, stream)
+                                                 n_heads, rank, scale, n_splits, part_o, part_ml, vrank, window, sink, stream)
   if (bm == 16 && rt >= 2 && narrow_tiles(n_tiles * n_splits)) {
 #define IFX_LN(RT) return launch_mma<1, RT, true>(q, ql, (bf16*)out, ol, (const bf16*)cache, page_stride, page_size, b, n_tiles, \
-                                                  n_heads, rank, scale, n_splits, part_o, part_ml, stream)
+                                                  n_heads, rank, scale, n_splits, part_o, part_ml, vrank, window, sink, stream)
     if (rt <= 2) IFX_LN(2);
     if (rt <= 4) IFX_LN(4);
     IFX_LN(8);
@@ -470,4 +488,15 @@ IFX_API int ifx_attn_latent_mma(const float* q, long long q_row, long long q_hea
   }
 #undef IFX_LM
   return IFX_ERR_UNSUPPORTED;
+}
+
+IFX_API int ifx_attn_latent_mma(const float* q, long long q_row, long long q_head, void* out, long long o_row,
+                                long long o_head, const void* cache, long long page_stride, int page_size,
+                                const int* block_tables, int bt_stride, const int* tile_entry, const int* tile_row0,
+                                int n_tiles, int bm, const int* entry_q_start, const int* entry_q_len,
+                                const int* entry_ctx_start, int n_heads, int rank, float scale, int n_splits,
+                                float* part_o, float* part_ml, cudaStream_t stream) {
+  return ifx_attn_latent_mma_ex(q, q_row, q_head, out, o_row, o_head, cache, page_stride, page_size, block_tables, bt_stride,
+                                tile_entry, tile_row0, n_tiles, bm, entry_q_start, entry_q_len, entry_ctx_start, n_heads, rank,
+                                scale, n_splits, part_o, part_ml, rank, 0, nullptr, stream);
 }

@@ -199,6 +199,8 @@ def _lib():
         lib.ifx_latent_rope_prep.argtypes = [c_void_p, c_ll, c_void_p, c_float, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                              c_void_p, c_void_p, c_ll, c_ll, c_void_p, c_int, c_ll, c_int, c_void_p, c_int,
                                              c_void_p]
+        lib.ifx_attn_latent_mma_ex.argtypes = list(lib.ifx_attn_latent_mma.argtypes[:-1]) + [c_int, c_int, c_void_p, c_void_p]
+        lib.ifx_attn_latent_mma_ex.restype = c_int
         for name in ("ifx_add_group_rmsnorm", "ifx_glu_clamped", "ifx_gla_scan", "ifx_attn_paged_generic_ex2",
                      "ifx_attn_latent_paged_ex", "ifx_latent_rope_prep"):
             getattr(lib, name).restype = c_int
@@ -1185,30 +1187,35 @@ def attn_latent_mma_splits(n_tiles: int, bm: int, rank: int, max_keys: int) -> i
 def attn_latent_mma(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, page_stride: int, page_size: int,
                     block_tables: torch.Tensor, tile_entry: torch.Tensor, tile_row0: torch.Tensor, n_tiles: int, bm: int,
                     entry_q_start: torch.Tensor, entry_q_len: torch.Tensor, entry_ctx_start: torch.Tensor, scale: float,
-                    n_splits: int = 1) -> torch.Tensor:
+                    n_splits: int = 1, window: int = 0, sink: Optional[torch.Tensor] = None) -> torch.Tensor:
     """:func:`attn_latent_paged` on the tensor cores, bfloat16 cache and result.
     A tile is ``bm`` (16, 32 or 64) consecutive (token, head) rows of one entry,
     counted token by token with the heads innermost; ``tile_row0`` is a tile's
     first row within its entry.  With ``n_splits`` > 1 every tile's keys are cut
-    into that many parts, which a second kernel merges."""
+    into that many parts, which a second kernel merges.  ``out`` may be narrower than ``q``
+    (``[N, heads, vrank]``, a multiple of 8): a cached row is then as wide as ``q``, its first
+    ``vrank`` columns are the latent, and the rest enters the scores only.  ``window`` and ``sink``
+    as in :func:`attn_latent_paged`."""
     _need(block_tables.dtype == torch.int32 and block_tables.dim() == 2 and block_tables.stride(1) == 1,
           "attn_latent_mma: block_tables int32 [R, B]")
     for t in (tile_entry, tile_row0, entry_q_start, entry_q_len, entry_ctx_start):
         _need(t.dtype == torch.int32, "attn_latent_mma: int32 metadata")
-    _need(q.dtype == torch.float32 and out.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and q.shape == out.shape,
-          "attn_latent_mma: q float32, out and cache bfloat16")
+    _need(q.dtype == torch.float32 and out.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16
+          and q.shape[:2] == out.shape[:2] and out.shape[2] <= q.shape[2], "attn_latent_mma: q float32, out and cache bfloat16")
     _need(bm in LATENT_MMA_TILES, "attn_latent_mma: tiles of 16, 32 or 64 rows")
-    n_heads, rank = q.shape[1], q.shape[2]
-    (q_row, q_head), (o_row, o_head) = _head_layout(q, n_heads, rank, "attn_latent_mma q"), _head_layout(out, n_heads, rank, "attn_latent_mma out")
+    n_heads, rank, vrank = q.shape[1], q.shape[2], out.shape[2]
+    _need(sink is None or (sink.dtype == torch.float32 and sink.is_contiguous() and sink.numel() == n_heads), "attn_latent_mma: sink float32 [heads]")
+    (q_row, q_head), (o_row, o_head) = _head_layout(q, n_heads, rank, "attn_latent_mma q"), _head_layout(out, n_heads, vrank, "attn_latent_mma out")
     _need(o_row % 2 == 0 and o_head % 2 == 0, "attn_latent_mma: out vectors on 4-byte boundaries")
     part_o = part_ml = None
     if n_splits > 1:
         part_o = torch.empty(n_tiles * n_splits * bm * rank, dtype=torch.float32, device=q.device)
         part_ml = torch.empty(n_tiles * n_splits * bm * 2, dtype=torch.float32, device=q.device)
-    _check(_lib().ifx_attn_latent_mma(_ptr(q), q_row, q_head, _ptr(out), o_row, o_head, _ptr(cache), page_stride, page_size,
-                                      _ptr(block_tables), block_tables.stride(0), _ptr(tile_entry), _ptr(tile_row0), n_tiles,
-                                      bm, _ptr(entry_q_start), _ptr(entry_q_len), _ptr(entry_ctx_start), n_heads, rank,
-                                      float(scale), n_splits, _ptr(part_o), _ptr(part_ml), _stream()), "attn_latent_mma")
+    _check(_lib().ifx_attn_latent_mma_ex(_ptr(q), q_row, q_head, _ptr(out), o_row, o_head, _ptr(cache), page_stride, page_size,
+                                         _ptr(block_tables), block_tables.stride(0), _ptr(tile_entry), _ptr(tile_row0), n_tiles,
+                                         bm, _ptr(entry_q_start), _ptr(entry_q_len), _ptr(entry_ctx_start), n_heads, rank,
+                                         float(scale), n_splits, _ptr(part_o), _ptr(part_ml), vrank, int(window), _ptr(sink),
+                                         _stream()), "attn_latent_mma")
     return out
 
 

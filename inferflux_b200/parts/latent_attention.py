@@ -88,6 +88,8 @@ class LatentAttention(Part):
     Position (with ``rot_dim``): a pair ``(cos, sin)`` of float32 ``[N, rot_dim / 2]`` tensors."""
 
     family = "mixer"
+    #: Switch for tests and measurements: the tensor-core kernel over the latents where the sizes allow it.
+    TENSOR_CORES = True
 
     def __init__(self, params, prefix, dtype, device):
         super().__init__(params, prefix, dtype, device)
@@ -295,9 +297,16 @@ class LatentAttention(Part):
                              ctx.page_size, ctx.slot_maps[g])
         self._per_head(q_plain.view(n, nh, self.dim), self.uk_t, out=q_rows[:, :, :r])
         o_lat = torch.empty((nh, n, r), dtype=x.dtype, device=x.device).transpose(0, 1)
-        ops.attn_latent_paged(q_rows, o_lat, cache, page_stride, ctx.page_size, ctx.block_tables[g], step.tile_entry,
-                              step.tile_q0, step.n_tiles, ctx.entry_q_start, ctx.entry_q_len, ctx.entry_ctx_start,
-                              self.scale, window=self.window, sink=self.sink)
+        if self.TENSOR_CORES and r % 8 == 0 and ops.attn_latent_mma_ok(self.width, cache):
+            keys = min(ctx.max_ctx_len, self.window + step.bm) if self.window else ctx.max_ctx_len     # what a tile can see
+            splits = ops.attn_latent_mma_splits(step.n_row_tiles, step.bm, self.width, keys)
+            ops.attn_latent_mma(q_rows, o_lat, cache, page_stride, ctx.page_size, ctx.block_tables[g], step.row_tile_entry,
+                                step.row_tile_row0, step.n_row_tiles, step.bm, ctx.entry_q_start, ctx.entry_q_len,
+                                ctx.entry_ctx_start, self.scale, splits, window=self.window, sink=self.sink)
+        else:
+            ops.attn_latent_paged(q_rows, o_lat, cache, page_stride, ctx.page_size, ctx.block_tables[g], step.tile_entry,
+                                  step.tile_q0, step.n_tiles, ctx.entry_q_start, ctx.entry_q_len, ctx.entry_ctx_start,
+                                  self.scale, window=self.window, sink=self.sink)
         heads = self._per_head(o_lat, self.uv)                                 # float32 [N, heads, vdim]
         if out is None:
             out = torch.empty((n, nh * self.vdim), dtype=x.dtype, device=x.device)

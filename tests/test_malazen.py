@@ -397,6 +397,24 @@ def test_latent_attention_alone(dtype, name, layer):
 
 @gpu
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [None, 700])
+def test_latent_attention_over_a_long_context(dtype, window):
+    """900 tokens without a window or with one of 700: single tokens whose keys the tensor-core kernel cuts into parts
+    that a second kernel merges, the sink counted once."""
+    cfg = _one_layer("C", 2)
+    cfg["layers"][0]["mixer"].pop("mask")
+    if window:
+        cfg["layers"][0]["mixer"]["mask"] = dict(size=window)
+    model, runner, w = _runner_for(cfg, dtype, 33, tokens=1024)
+    portions = [600, 1, 1, 290, 1, 1, 2, 1, 1, 1, 1]
+    x = _rand((sum(portions), cfg["width"]), 34).to(dtype)
+    want = plain.latent_attention(x.double(), w, "l0.mix", cfg["layers"][0]["mixer"], cfg["norm"]["eps"])
+    got = _mixer_in_portions(model, runner, 0, x, portions, dtype)
+    assert _rel(got, want) < PTOL[dtype]
+
+
+@gpu
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("rank,rot,width", [(16, 12, 64), (56, 8, 160)])
 def test_latent_window_edges_and_sink_with_one_score_that_stands_out(dtype, rank, rot, width):
     """210 tokens, a window of 40, pages of 16.  Head 0's rotated query part is read off the token's first ``rot``

@@ -226,7 +226,7 @@ def malazen_config(size: str, layers: int):
     """A Malazen config.json at the widths of one of the family sizes above: layers in turn a pair of mixers side by side
     (attention with the family's heads and kv heads of 128, biases, a query temperature and a toll on distance, beside
     gated linear attention with half as many heads of 128 x 128 and a decay projection through 16) and latent attention
-    (the family's heads of 128 plain and 64 rotated dimensions over latents of 512, values of 128, a window of 1,024,
+    (the family's heads of 128 plain and 64 rotated dimensions over latents of 448, a cached row of 512, values of 128, a window of 1,024,
     stretched frequencies, a sink per head); every layer with a clamped gated feed-forward of the family's width; the
     norms taken in four groups; no loop."""
     _, hidden, heads, kv_heads, inter, vocab, _ = SIZES[size]
@@ -234,7 +234,7 @@ def malazen_config(size: str, layers: int):
     right = dict(heads=max(1, heads // 2), dim=128, vdim=128, tau=16.0)
     pair = dict(type="parallel", mixer=dict(left=left, right=right, left_scale=1.0, right_scale=1.0), mlp=dict(kind="dense", ff=inter, limit=7.0))
     latent = dict(type="latent_attention", mlp=dict(kind="dense", ff=inter, limit=7.0), mixer=dict(
-        heads=heads, dim=128, rot_dim=64, vdim=128, kv_rank=512, scale=192 ** -0.5, mask=dict(size=1024),
+        heads=heads, dim=128, rot_dim=64, vdim=128, kv_rank=448, scale=192 ** -0.5, mask=dict(size=1024),
         rot=dict(dims=64, base=500000.0, scaling=dict(factor=4.0, original=8192, fast=16.0, slow=2.0))))
     return dict(architecture="Malazen", width=hidden, vocab=vocab, norm=dict(eps=1e-6, groups=4),
                 layers=[pair if i % 2 == 0 else latent for i in range(layers)])

@@ -154,6 +154,10 @@ struct PrefillOptions {
   int keep_first;
   int sink;
   const float* gate; int gate_parts; long long gate_part_stride; int gate_stride;
+  // a query temperature (the query at position p counts 1 + coef * ln(floor((p + 1) / every) + 1) times; every = 0:
+  // none) and a toll on distance (the score of key j loses r1[head] * ln(1 + r2[head] * (p - j)), after the cap;
+  // null: none)
+  float q_temp_coef; int q_temp_every; const float* dist_r1; const float* dist_r2;
 };
 
 // tanh from one exponential: (e^2x - 1) / (e^2x + 1), the argument held where e^2x neither overflows nor
@@ -213,9 +217,12 @@ attn_prefill_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
   // sums of a row's four lanes are added at the end, so one lane holds it)
   float mrow[2] = {opt.sink ? 0.0f : -INFINITY, opt.sink ? 0.0f : -INFINITY};
   float lrow[2] = {opt.sink && t4 == 0 ? 1.0f : 0.0f, opt.sink && t4 == 0 ? 1.0f : 0.0f};
-  // capped scores are formed from the scaled ones before the softmax; their exponents need no further scale
-  const float sl2 = opt.softcap > 0.0f ? LOG2E : scale * LOG2E;
+  // capped scores are formed from the scaled ones before the softmax; their exponents need no further scale.
+  // The same goes for scores under a temperature or a toll ("shaped": scaled per row, capped, the toll taken off).
+  const bool shaped = opt.q_temp_every > 0 || opt.dist_r1 != nullptr;
+  const float sl2 = (opt.softcap > 0.0f || shaped) ? LOG2E : scale * LOG2E;
   const float cap_in = opt.softcap > 0.0f ? scale / opt.softcap : 0.0f;
+  const float toll1 = opt.dist_r1 ? opt.dist_r1[head] : 0.0f, toll2 = opt.dist_r1 ? opt.dist_r2[head] : 0.0f;
 
   const int kend = pos0 + rows;                                  // keys [.., kend) may be seen
   const int kfirst = window > 0 ? max(0, pos0 - window + 1) : 0; // first key the first row may see
@@ -286,7 +293,24 @@ attn_prefill_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
         }
       }
       // mask (diagonal, window and edge tiles only), row maxima of the raw scores
-      if (opt.softcap > 0.0f) {
+      if (shaped) {
+        float row_scale[2] = {scale, scale};
+        if (opt.q_temp_every > 0) {
+          row_scale[0] *= 1.0f + opt.q_temp_coef * logf((float)((pa_row + 1) / opt.q_temp_every + 1));
+          row_scale[1] *= 1.0f + opt.q_temp_coef * logf((float)((pb_row + 1) / opt.q_temp_every + 1));
+        }
+#pragma unroll
+        for (int n = 0; n < BK / 8; ++n) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const int dist = ((c & 2) ? pb_row : pa_row) - (key0 + n * 8 + t4 * 2 + (c & 1));
+            float v = s[n][c] * row_scale[c >> 1];
+            if (opt.softcap > 0.0f) v = opt.softcap * tanh_exp(v / opt.softcap);
+            if (opt.dist_r1) v -= toll1 * __logf(fmaf(toll2, (float)max(dist, 0), 1.0f));
+            s[n][c] = v;
+          }
+        }
+      } else if (opt.softcap > 0.0f) {
 #pragma unroll
         for (int n = 0; n < BK / 8; ++n) {
 #pragma unroll
@@ -1188,20 +1212,22 @@ int launch_decode_even(const void* q, long long q_stride, void* out, long long o
 
 // head_dim 64 or 128; page_size a power of two; q rows 4-byte aligned.
 // Query tiles are 64 tokens of one entry (tile_entry / tile_q0).
-IFX_API int ifx_attn_prefill_bf16_ex(const void* q, long long q_stride, void* out, long long out_stride,
+// q_temp_every > 0: a query temperature; dist_r1 / dist_r2 ([n_heads] float32 or null): a toll on distance.
+IFX_API int ifx_attn_prefill_bf16_ex2(const void* q, long long q_stride, void* out, long long out_stride,
                                   void* k_layer, void* v_layer, long long page_stride, int page_size,
                                   const int* block_tables, int bt_stride, const int* tile_entry, const int* tile_q0,
                                   int n_tiles, const int* entry_q_start, const int* entry_q_len,
                                   const int* entry_ctx_start, int n_heads, int n_kv, int head_dim, float scale,
                                   int window, float softcap, int keep_first, int sink, const float* gate, int gate_parts,
-                                  long long gate_part_stride, int gate_stride, cudaStream_t stream) {
+                                  long long gate_part_stride, int gate_stride, float q_temp_coef, int q_temp_every,
+                                  const float* dist_r1, const float* dist_r2, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (n_kv < 1 || n_heads % n_kv || n_tiles > 65535) return IFX_ERR_UNSUPPORTED;
   if (page_size <= 0 || (page_size & (page_size - 1))) return IFX_ERR_UNSUPPORTED;
   if ((q_stride & 1) || (out_stride & 1) || ((uintptr_t)q & 3) || ((uintptr_t)out & 3)) return IFX_ERR_ALIGNMENT;
   if ((page_stride & 7) || ((uintptr_t)k_layer & 15) || ((uintptr_t)v_layer & 15)) return IFX_ERR_ALIGNMENT;
-  if (softcap < 0.0f || keep_first < 0) return IFX_ERR_UNSUPPORTED;
-  PrefillOptions opt{softcap, keep_first, sink, gate, gate_parts, gate_part_stride, gate_stride};
+  if (softcap < 0.0f || keep_first < 0 || q_temp_every < 0 || (dist_r1 != nullptr) != (dist_r2 != nullptr)) return IFX_ERR_UNSUPPORTED;
+  PrefillOptions opt{softcap, keep_first, sink, gate, gate_parts, gate_part_stride, gate_stride, q_temp_coef, q_temp_every, dist_r1, dist_r2};
   PagedKV kv = make_kv(k_layer, v_layer, page_stride, page_size, head_dim);
   AttnMeta m{block_tables, bt_stride, entry_q_start, entry_q_len, entry_ctx_start};
   if (head_dim == 128)
@@ -1209,6 +1235,19 @@ IFX_API int ifx_attn_prefill_bf16_ex(const void* q, long long q_stride, void* ou
   if (head_dim == 64)
     return launch_prefill<64>(q, q_stride, out, out_stride, kv, m, tile_entry, tile_q0, n_tiles, n_heads, n_kv, scale, window, opt, stream);
   return IFX_ERR_UNSUPPORTED;
+}
+
+IFX_API int ifx_attn_prefill_bf16_ex(const void* q, long long q_stride, void* out, long long out_stride,
+                                  void* k_layer, void* v_layer, long long page_stride, int page_size,
+                                  const int* block_tables, int bt_stride, const int* tile_entry, const int* tile_q0,
+                                  int n_tiles, const int* entry_q_start, const int* entry_q_len,
+                                  const int* entry_ctx_start, int n_heads, int n_kv, int head_dim, float scale,
+                                  int window, float softcap, int keep_first, int sink, const float* gate, int gate_parts,
+                                  long long gate_part_stride, int gate_stride, cudaStream_t stream) {
+  return ifx_attn_prefill_bf16_ex2(q, q_stride, out, out_stride, k_layer, v_layer, page_stride, page_size, block_tables, bt_stride,
+                                   tile_entry, tile_q0, n_tiles, entry_q_start, entry_q_len, entry_ctx_start, n_heads, n_kv,
+                                   head_dim, scale, window, softcap, keep_first, sink, gate, gate_parts, gate_part_stride,
+                                   gate_stride, 0.0f, 0, nullptr, nullptr, stream);
 }
 
 IFX_API int ifx_attn_prefill_bf16(const void* q, long long q_stride, void* out, long long out_stride,

@@ -190,7 +190,10 @@ def _lib():
         lib.ifx_glu_clamped.argtypes = [c_void_p, c_int, c_ll, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_float,
                                         c_void_p]
         lib.ifx_gla_scan.argtypes = [c_void_p, c_ll, c_int, c_int, c_int, c_void_p, c_ll, c_void_p, c_float, c_float, c_void_p,
-                                     c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_ll, c_int, c_int, c_int, c_void_p]
+                                     c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_ll, c_int, c_int, c_int,
+                                     c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p]
+        lib.ifx_gla_segment.argtypes = []
+        lib.ifx_gla_segment.restype = c_int
         lib.ifx_attn_paged_generic_ex2.argtypes = list(lib.ifx_attn_paged_generic_ex.argtypes[:-1]) + [
             c_float, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
         lib.ifx_attn_latent_paged_ex.argtypes = [c_void_p, c_ll, c_ll, c_void_p, c_ll, c_ll, c_void_p, c_int, c_ll, c_int,
@@ -199,6 +202,8 @@ def _lib():
         lib.ifx_latent_rope_prep.argtypes = [c_void_p, c_ll, c_void_p, c_float, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                              c_void_p, c_void_p, c_ll, c_ll, c_void_p, c_int, c_ll, c_int, c_void_p, c_int,
                                              c_void_p]
+        lib.ifx_attn_prefill_bf16_ex2.argtypes = list(lib.ifx_attn_prefill_bf16_ex.argtypes[:-1]) + [c_float, c_int, c_void_p, c_void_p, c_void_p]
+        lib.ifx_attn_prefill_bf16_ex2.restype = c_int
         lib.ifx_attn_latent_mma_ex.argtypes = list(lib.ifx_attn_latent_mma.argtypes[:-1]) + [c_int, c_int, c_void_p, c_void_p]
         lib.ifx_attn_latent_mma_ex.restype = c_int
         for name in ("ifx_add_group_rmsnorm", "ifx_glu_clamped", "ifx_gla_scan", "ifx_attn_paged_generic_ex2",
@@ -1368,20 +1373,25 @@ def attn_prefill_options_bf16(q: torch.Tensor, q_stride: int, out: torch.Tensor,
                               tile_q0: torch.Tensor, n_tiles: int, entry_q_start: torch.Tensor, entry_q_len: torch.Tensor,
                               entry_ctx_start: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, scale: float,
                               window: int, softcap: float = 0.0, keep_first: int = 0, sink: bool = False,
-                              gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+                              gate: Optional[torch.Tensor] = None, q_temp=None, distance_toll=None) -> torch.Tensor:
     """:func:`attn_prefill_bf16` (tensor cores, bfloat16, keys and values both ``head_dim`` = 64 or 128 wide, query
-    tiles of 64 tokens) with the options of :func:`attn_paged_options`."""
+    tiles of 64 tokens) with the options of :func:`attn_paged_options` (all but the sink's own score)."""
+    coef, every = (float(q_temp[0]), int(q_temp[1])) if q_temp else (0.0, 0)
+    r1, r2 = distance_toll if distance_toll else (None, None)
+    for t in (r1, r2):
+        _need(t is None or (t.dtype == torch.float32 and t.is_contiguous() and t.numel() == n_heads), "attn: per-head numbers float32 [heads]")
     _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_layer.dtype == torch.bfloat16,
           "attn_prefill_options_bf16: bfloat16 operands")
     _need(head_dim in FAST_ATTENTION_HEAD_DIMS, f"attn_prefill_options_bf16: head_dim {head_dim} not in {FAST_ATTENTION_HEAD_DIMS}")
     _need(block_tables.dtype == torch.int32 and block_tables.stride(1) == 1, "attn: block_tables int32 [R, B]")
     gp, g_parts, g_pstride, g_stride = _gate_slices(gate, n_heads * head_dim, "attn_prefill_options_bf16")
-    _check(_lib().ifx_attn_prefill_bf16_ex(_ptr(q), q_stride, _ptr(out), out.stride(0), _ptr(k_layer), _ptr(v_layer),
+    _check(_lib().ifx_attn_prefill_bf16_ex2(_ptr(q), q_stride, _ptr(out), out.stride(0), _ptr(k_layer), _ptr(v_layer),
                                            page_stride, page_size, _ptr(block_tables), block_tables.stride(0),
                                            _ptr(tile_entry), _ptr(tile_q0), n_tiles, _ptr(entry_q_start),
                                            _ptr(entry_q_len), _ptr(entry_ctx_start), n_heads, n_kv, head_dim,
                                            float(scale), int(window), float(softcap), int(keep_first), 1 if sink else 0,
-                                           gp, g_parts, g_pstride, g_stride, _stream()), "attn_prefill_options_bf16")
+                                           gp, g_parts, g_pstride, g_stride, coef, every, _ptr(r1), _ptr(r2), _stream()),
+           "attn_prefill_options_bf16")
     return out
 
 
@@ -1736,11 +1746,15 @@ def glu_clamped(z: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor
 
 def gla_scan(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, z: torch.Tensor, z_bias: torch.Tensor, tau: float,
              q_scale: float, state: torch.Tensor, entry_q_start: torch.Tensor, entry_q_len: torch.Tensor,
-             entry_slot: torch.Tensor, n_entries: int, out: torch.Tensor, heads: int, dim: int, vdim: int) -> torch.Tensor:
+             entry_slot: torch.Tensor, n_entries: int, out: torch.Tensor, heads: int, dim: int, vdim: int,
+             seg_entry: Optional[torch.Tensor] = None, seg_t0: Optional[torch.Tensor] = None,
+             entry_first_seg: Optional[torch.Tensor] = None, n_segments: int = 0) -> torch.Tensor:
     """Gated linear attention, float32.  Per head ``alpha = sigmoid(z + z_bias)^(1 / tau)`` (one per key channel),
     ``S <- diag(alpha) S + k v^T``, ``o = S^T (q * q_scale)``.  ``proj`` float32 rows hold q, k (``heads * dim`` each)
     and v (``heads * vdim``) from the given columns; ``z`` float32 rows ``[N, heads * dim]``; ``state [slots, heads,
-    dim, vdim]``; ``out`` float32 ``[N, heads * vdim]``."""
+    dim, vdim]``; ``out`` float32 ``[N, heads * vdim]``.  With ``n_segments`` > 0 the step is cut into segments of
+    :func:`gla_segment` tokens (``seg_entry``, ``seg_t0``, ``entry_first_seg``: int32) that run side by side, their
+    starting states found one after the other in between; without, every entry is walked from its slot in one go."""
     n = proj.shape[0]
     _need(proj.dtype == torch.float32 and proj.stride(1) == 1 and z.dtype == torch.float32 and z.stride(1) == 1
           and tuple(z.shape) == (n, heads * dim), "gla_scan: float32 rows")
@@ -1749,7 +1763,21 @@ def gla_scan(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, z: torch.Te
           "gla_scan: state float32 [slots, heads, dim, vdim]")
     _need(out.dtype == torch.float32 and out.stride(1) == 1 and tuple(out.shape) == (n, heads * vdim), "gla_scan: out")
     _need(max(q_col, k_col) + heads * dim <= proj.shape[1] and v_col + heads * vdim <= proj.shape[1], "gla_scan: columns beyond the row")
+    seg_state = seg_decay = None
+    if n_segments > 0:
+        seg_state = torch.empty((n_segments, heads, dim, vdim), dtype=torch.float32, device=proj.device)
+        seg_decay = torch.empty((n_segments, heads, dim), dtype=torch.float32, device=proj.device)
     _check(_lib().ifx_gla_scan(_ptr(proj), proj.stride(0), q_col, k_col, v_col, _ptr(z), z.stride(0), _ptr(z_bias),
                                1.0 / float(tau), float(q_scale), _ptr(state), _ptr(entry_q_start), _ptr(entry_q_len),
-                               _ptr(entry_slot), n_entries, _ptr(out), out.stride(0), heads, dim, vdim, _stream()), "gla_scan")
+                               _ptr(entry_slot), n_entries, _ptr(out), out.stride(0), heads, dim, vdim, _ptr(seg_entry),
+                               _ptr(seg_t0), _ptr(entry_first_seg), int(n_segments), _ptr(seg_state), _ptr(seg_decay),
+                               _stream()), "gla_scan")
+    if n_segments > 0:
+        global launch_count
+        launch_count += 2
     return out
+
+
+def gla_segment() -> int:
+    """Tokens per segment of the gated linear attention scan."""
+    return int(_lib().ifx_gla_segment())

@@ -9,10 +9,12 @@ divided by its root mean square and multiplied by a weight ``vdim`` long that al
 side are multiplied by silu(W_g h) and projected.  q, k, v, g and the narrow a1 are one stacked projection whose
 sums stay float32; the second decay projection runs in float32 on those sums (its matrix is small), and decays,
 state, outputs and the norm are float32 in either engine type.  The state lives in the request's state slot, so a
-prompt may be cut anywhere.
+prompt may be cut anywhere; a portion longer than a segment is cut into segments that run side by side (the
+recurrence is linear in S).
 """
 from __future__ import annotations
 
+from dataclasses import dataclass
 from typing import Any, Dict, List
 
 import torch
@@ -24,12 +26,24 @@ from .base import Part, RunInfo, StateNeed
 from .linear import Linear
 
 
+@dataclass
+class GlaStep:
+    """The step cut into segments for the scan kernels: int32 device tensors; ``n_segments`` 0 = every entry fits
+    one segment and is walked from its slot."""
+
+    seg_entry: torch.Tensor
+    seg_t0: torch.Tensor
+    entry_first_seg: torch.Tensor
+    n_segments: int
+
+
 class GatedLinearAttention(Part):
     """params: ``hidden``, ``heads``, ``dim``, ``vdim``, ``tau``, ``q_scale`` (None = ``dim^-1/2``), ``decay_rank``
     (0 = whatever the stored ``a1`` has), ``eps`` (of the per-head norm), ``name`` (tensors
     ``<prefix>.<name>.{q,k,v,g,o,a1,a2,a2.b,norm}``).  State: ``gla`` float32 ``[heads, dim, vdim]``."""
 
     family = "mixer"
+    describe_key = "gla_segments"
 
     def __init__(self, params, prefix, dtype, device):
         super().__init__(params, prefix, dtype, device)
@@ -78,6 +92,17 @@ class GatedLinearAttention(Part):
         self.norm_w = tensors.pop(n("norm")).to(torch.float32).repeat(self.heads).contiguous()
         self.o = Linear(tensors.pop(n("o")))
 
+    def describe_step(self, layout, put) -> GlaStep:
+        seg = ops.gla_segment() if torch.device(self.device).type == "cuda" else 64
+        if all(int(layout.q_len[i]) <= seg for i in range(layout.n_entries)):
+            return GlaStep(put([]), put([]), put([]), 0)
+        seg_entry, seg_t0, first = [], [], []
+        for i in range(layout.n_entries):
+            first.append(len(seg_entry))
+            for t0 in range(0, int(layout.q_len[i]), seg):
+                seg_entry.append(i), seg_t0.append(t0)
+        return GlaStep(put(seg_entry), put(seg_t0), put(first), len(seg_entry))
+
     @property
     def inner_width(self) -> int:
         return self.heads * self.vdim
@@ -88,8 +113,10 @@ class GatedLinearAttention(Part):
         proj = self.stacked.forward(x, out_dtype=torch.float32)               # [q | k | v | g | a1]
         z = self.a2.forward(proj[:, 2 * hd + 2 * hv:], out_dtype=torch.float32)
         o = torch.empty((n, hv), dtype=torch.float32, device=dev)
+        step: GlaStep = ctx.extras[self.describe_key]
         ops.gla_scan(proj, 0, hd, 2 * hd, z, self.a2_bias, self.tau, self.q_scale, run.states["gla"], ctx.entry_q_start,
-                     ctx.entry_q_len, ctx.entry_slot, ctx.n_entries, o, self.heads, self.dim, self.vdim)
+                     ctx.entry_q_len, ctx.entry_slot, ctx.n_entries, o, self.heads, self.dim, self.vdim, step.seg_entry,
+                     step.seg_t0, step.entry_first_seg, step.n_segments)
         if out is None:
             out = torch.empty((n, hv), dtype=x.dtype, device=dev)
         return ops.head_norm_gate(o, proj[:, 2 * hd + hv:2 * hd + 2 * hv], self.norm_w, out, self.heads, self.vdim, self.eps,

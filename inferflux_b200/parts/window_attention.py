@@ -257,9 +257,9 @@ class WindowAttention(Part):
             ops.attn_paged_options(q, q.stride(0), out, *pages, step.single_entry, step.single_q0, step.n_single, *common, *rest,
                                    single_tokens=True, **more)
         if step.n_chunk and (self.TENSOR_CORES and x.dtype == torch.bfloat16 and self.dim == self.vdim and out.is_contiguous()
-                             and self.dim in ops.FAST_ATTENTION_HEAD_DIMS and not self.q_temp and not self.toll):
+                             and self.dim in ops.FAST_ATTENTION_HEAD_DIMS):
             ops.attn_prefill_options_bf16(q, q.stride(0), out, *pages, step.chunk_entry, step.chunk_q0, step.n_chunk, *common,
-                                          self.softcap, self.keep_first, self.sink, gate)      # portions on tensor cores
+                                          self.softcap, self.keep_first, self.sink, gate, **more)      # portions on tensor cores
         elif step.n_tiles:
             ops.attn_paged_options(q, q.stride(0), out, *pages, step.tile_entry, step.tile_q0, step.n_tiles, *common, *rest, **more)
         return out

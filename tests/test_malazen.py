@@ -290,7 +290,7 @@ def test_biased_attention_alone(dtype, name, layer):
 
 @gpu
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("dim,vdim,width", [(16, 12, 64), (64, 64, 160)])
+@pytest.mark.parametrize("dim,vdim,width", [(16, 12, 64), (64, 64, 160), (128, 128, 320)])
 def test_a_key_far_back_under_the_toll(dtype, dim, vdim, width):
     """400 tokens, pages of 16.  Head 0's query is the token's first ``dim`` numbers and the key the next ``dim``.  Each
     of the last eight tokens gets a query that matches the key of one chosen earlier token and no other: the very

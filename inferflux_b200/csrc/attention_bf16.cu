@@ -454,6 +454,13 @@ struct QkvPrep {
   long long part_stride;    // n_tokens * width
 };
 
+// What shapes a decoded token's scores beyond the scale (all off for plain attention): a query temperature (the
+// query at position p counts 1 + coef * ln(floor((p + 1) / every) + 1) times; every = 0: none) and a toll on
+// distance (the score of key j loses r1[head] * ln(1 + r2[head] * (p - j)); null: none).
+struct ScoreShape {
+  float q_temp_coef; int q_temp_every; const float* dist_r1; const float* dist_r2;
+};
+
 // PREP: the kernel takes the place of the bias/rotation/cache-write kernel for the token it decodes.  Every
 // block adds the bias to and rotates the query heads it works on (into shared memory); the block whose
 // part of the keys ends with the token's own position does the same for the key, adds the bias to the
@@ -464,7 +471,8 @@ __global__ void __launch_bounds__(128)
 attn_decode_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out, long long out_stride,
                         PagedKV kv, AttnMeta m, const int* __restrict__ dec_entries,
                         float* __restrict__ part_o, float* __restrict__ part_ml,
-                        int n_heads, int n_kv, int head_chunks, float scale, int window, int n_splits, QkvPrep prep) {
+                        int n_heads, int n_kv, int head_chunks, float scale, int window, int n_splits, QkvPrep prep,
+                        ScoreShape shape) {
   // Up to pdl_wait() below the block reads only what no kernel of the step writes (the step's
   // metadata) and keys and values of tokens older than the one being decoded.
   pdl_launch_dependents();
@@ -580,7 +588,20 @@ attn_decode_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
         qb[k][1] = g < nrows ? pq[k * 8 + 4 + t4] : 0u;
       }
     }
-    const float sl2 = scale * LOG2E;
+    // shaped scores (a temperature, a toll) are brought to their final form before the softmax; their exponents
+    // need no further scale
+    const bool shaped = shape.q_temp_every > 0 || shape.dist_r1 != nullptr;
+    const float sl2 = shaped ? LOG2E : scale * LOG2E;
+    float row_scale = scale, toll1[2] = {0.0f, 0.0f}, toll2[2] = {0.0f, 0.0f};
+    if (shape.q_temp_every > 0) row_scale *= 1.0f + shape.q_temp_coef * logf((float)(len / shape.q_temp_every + 1));
+    if (shape.dist_r1) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int head = min(h0 + 2 * t4 + h, n_heads - 1);     // columns beyond the block's heads are never written
+        toll1[h] = shape.dist_r1[head];
+        toll2[h] = shape.dist_r2[head];
+      }
+    }
     if (!early) first_tiles();
     const unsigned ring_addr = (unsigned)__cvta_generic_to_shared(ring);
     unsigned koff[KS], voff[KS];                                // this lane's ldmatrix rows within a stage, swizzle included
@@ -618,6 +639,13 @@ attn_decode_bf16_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
         }
 #pragma unroll
         for (int c = 0; c < 4; ++c) s[c] += s1[c];
+      }
+      if (shaped) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int dist = max(len - 1 - (key0 + g + (c >> 1) * 8), 0);
+          s[c] = s[c] * row_scale - toll1[c & 1] * __logf(fmaf(toll2[c & 1], (float)dist, 1.0f));
+        }
       }
       const bool in0 = key0 + g >= kb && key0 + g < ke, in1 = key0 + g + 8 >= kb && key0 + g + 8 < ke;
       if (!in0) { s[0] = -INFINITY; s[1] = -INFINITY; }
@@ -1146,7 +1174,7 @@ int launch_prefill(const void* q, long long q_stride, void* out, long long out_s
 template <int HD, bool PREP>
 int launch_decode(const void* q, long long q_stride, void* out, long long out_stride, PagedKV kv, AttnMeta m,
                   const int* dec_entries, int n_dec, float* part_o, float* part_ml, int n_heads, int n_kv,
-                  float scale, int window, int n_splits, QkvPrep prep, cudaStream_t stream) {
+                  float scale, int window, int n_splits, QkvPrep prep, cudaStream_t stream, ScoreShape shape = ScoreShape{}) {
   const size_t stage_bytes = (size_t)DSTAGES * 2 * 64 * HD * sizeof(bf16);
   const size_t red_bytes = (size_t)4 * 8 * HD * sizeof(float) + 4 * 8 * 2 * sizeof(float);
   const size_t smem = stage_bytes > red_bytes ? stage_bytes : red_bytes;
@@ -1158,7 +1186,7 @@ int launch_decode(const void* q, long long q_stride, void* out, long long out_st
   const int ratio = n_heads / n_kv;
   const int head_chunks = (ratio + 7) / 8;
   int rc = launch_pdl(kern, dim3(n_dec, n_kv * head_chunks, n_splits), dim3(128), smem, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride, kv, m, dec_entries, part_o, part_ml, n_heads, n_kv,
-      head_chunks, scale, window, n_splits, prep);
+      head_chunks, scale, window, n_splits, prep, shape);
   if (!rc) rc = IFX_LAUNCH_CHECK();
   if (rc || n_splits == 1) return rc;
   rc = launch_pdl(attn_decode_merge_kernel, dim3(n_dec, n_heads), dim3(HD < 128 ? HD : 128), 0, stream, part_o, part_ml, (bf16*)out, out_stride, dec_entries, m.entry_q_start, n_heads, HD, n_splits);
@@ -1263,13 +1291,17 @@ IFX_API int ifx_attn_prefill_bf16(const void* q, long long q_stride, void* out, 
 
 // Scratch: part_o float32 [n_dec * n_heads * n_splits * head_dim], part_ml float32
 // [n_dec * n_heads * n_splits * 2] (unused when n_splits == 1).
-IFX_API int ifx_attn_decode_bf16(const void* q, long long q_stride, void* out, long long out_stride,
-                                 void* k_layer, void* v_layer, long long page_stride, int page_size,
-                                 const int* block_tables, int bt_stride, const int* dec_entries, int n_dec,
-                                 const int* entry_q_start, const int* entry_q_len, const int* entry_ctx_start,
-                                 float* part_o, float* part_ml, int n_heads, int n_kv, int head_dim, float scale,
-                                 int window, int n_splits, cudaStream_t stream) {
+// q_temp_every > 0: a query temperature; dist_r1 / dist_r2 ([n_heads] float32 or null): a toll on distance.
+IFX_API int ifx_attn_decode_bf16_ex(const void* q, long long q_stride, void* out, long long out_stride,
+                                    void* k_layer, void* v_layer, long long page_stride, int page_size,
+                                    const int* block_tables, int bt_stride, const int* dec_entries, int n_dec,
+                                    const int* entry_q_start, const int* entry_q_len, const int* entry_ctx_start,
+                                    float* part_o, float* part_ml, int n_heads, int n_kv, int head_dim, float scale,
+                                    int window, int n_splits, float q_temp_coef, int q_temp_every, const float* dist_r1,
+                                    const float* dist_r2, cudaStream_t stream) {
   if (n_dec <= 0) return 0;
+  if (q_temp_every < 0 || (dist_r1 != nullptr) != (dist_r2 != nullptr)) return IFX_ERR_UNSUPPORTED;
+  const ScoreShape shape{q_temp_coef, q_temp_every, dist_r1, dist_r2};
   if (n_kv < 1 || n_heads % n_kv || n_splits < 1 || n_splits > 65535) return IFX_ERR_UNSUPPORTED;
   if (page_size <= 0 || (page_size & (page_size - 1))) return IFX_ERR_UNSUPPORTED;
   if ((q_stride & 1) || ((uintptr_t)q & 3)) return IFX_ERR_ALIGNMENT;
@@ -1278,10 +1310,21 @@ IFX_API int ifx_attn_decode_bf16(const void* q, long long q_stride, void* out, l
   PagedKV kv = make_kv(k_layer, v_layer, page_stride, page_size, head_dim);
   AttnMeta m{block_tables, bt_stride, entry_q_start, entry_q_len, entry_ctx_start};
   if (head_dim == 128)
-    return launch_decode<128, false>(q, q_stride, out, out_stride, kv, m, dec_entries, n_dec, part_o, part_ml, n_heads, n_kv, scale, window, n_splits, QkvPrep{}, stream);
+    return launch_decode<128, false>(q, q_stride, out, out_stride, kv, m, dec_entries, n_dec, part_o, part_ml, n_heads, n_kv, scale, window, n_splits, QkvPrep{}, stream, shape);
   if (head_dim == 64)
-    return launch_decode<64, false>(q, q_stride, out, out_stride, kv, m, dec_entries, n_dec, part_o, part_ml, n_heads, n_kv, scale, window, n_splits, QkvPrep{}, stream);
+    return launch_decode<64, false>(q, q_stride, out, out_stride, kv, m, dec_entries, n_dec, part_o, part_ml, n_heads, n_kv, scale, window, n_splits, QkvPrep{}, stream, shape);
   return IFX_ERR_UNSUPPORTED;
+}
+
+IFX_API int ifx_attn_decode_bf16(const void* q, long long q_stride, void* out, long long out_stride,
+                                 void* k_layer, void* v_layer, long long page_stride, int page_size,
+                                 const int* block_tables, int bt_stride, const int* dec_entries, int n_dec,
+                                 const int* entry_q_start, const int* entry_q_len, const int* entry_ctx_start,
+                                 float* part_o, float* part_ml, int n_heads, int n_kv, int head_dim, float scale,
+                                 int window, int n_splits, cudaStream_t stream) {
+  return ifx_attn_decode_bf16_ex(q, q_stride, out, out_stride, k_layer, v_layer, page_stride, page_size, block_tables, bt_stride,
+                                 dec_entries, n_dec, entry_q_start, entry_q_len, entry_ctx_start, part_o, part_ml, n_heads, n_kv,
+                                 head_dim, scale, window, n_splits, 0.0f, 0, nullptr, nullptr, stream);
 }
 
 // The same for a step of single tokens only, with the work of ifx_qkv_rope_kv_write folded in: qkv is the

@@ -202,6 +202,8 @@ def _lib():
         lib.ifx_latent_rope_prep.argtypes = [c_void_p, c_ll, c_void_p, c_float, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                              c_void_p, c_void_p, c_ll, c_ll, c_void_p, c_int, c_ll, c_int, c_void_p, c_int,
                                              c_void_p]
+        lib.ifx_attn_decode_bf16_ex.argtypes = list(lib.ifx_attn_decode_bf16.argtypes[:-1]) + [c_float, c_int, c_void_p, c_void_p, c_void_p]
+        lib.ifx_attn_decode_bf16_ex.restype = c_int
         lib.ifx_attn_prefill_bf16_ex2.argtypes = list(lib.ifx_attn_prefill_bf16_ex.argtypes[:-1]) + [c_float, c_int, c_void_p, c_void_p, c_void_p]
         lib.ifx_attn_prefill_bf16_ex2.restype = c_int
         lib.ifx_attn_latent_mma_ex.argtypes = list(lib.ifx_attn_latent_mma.argtypes[:-1]) + [c_int, c_int, c_void_p, c_void_p]
@@ -681,11 +683,16 @@ def attn_decode_bf16(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_layer:
                      dec_entries: torch.Tensor, n_dec: int, entry_q_start: torch.Tensor,
                      entry_q_len: torch.Tensor, entry_ctx_start: torch.Tensor, part_o: Optional[torch.Tensor],
                      part_ml: Optional[torch.Tensor], n_heads: int, n_kv: int, head_dim: int, scale: float,
-                     window: int, n_splits: int) -> torch.Tensor:
+                     window: int, n_splits: int, q_temp=None, distance_toll=None) -> torch.Tensor:
     """Tensor-core attention of single decoded tokens (entries listed in
     dec_entries), the keys split ``n_splits`` ways and merged.  Scratch:
     part_o float32 [n_dec * n_heads * n_splits * head_dim], part_ml float32
-    [n_dec * n_heads * n_splits * 2]."""
+    [n_dec * n_heads * n_splits * 2].  ``q_temp`` and ``distance_toll`` as in
+    :func:`attn_paged_options`."""
+    coef, every = (float(q_temp[0]), int(q_temp[1])) if q_temp else (0.0, 0)
+    r1, r2 = distance_toll if distance_toll else (None, None)
+    for t in (r1, r2):
+        _need(t is None or (t.dtype == torch.float32 and t.is_contiguous() and t.numel() == n_heads), "attn: per-head numbers float32 [heads]")
     _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_layer.dtype == torch.bfloat16,
           "attn_decode_bf16: bfloat16 operands")
     _need(head_dim in FAST_ATTENTION_HEAD_DIMS, f"attn_decode_bf16: head_dim {head_dim} not in {FAST_ATTENTION_HEAD_DIMS}")
@@ -698,11 +705,12 @@ def attn_decode_bf16(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_layer:
     global launch_count
     if n_splits > 1:
         launch_count += 1          # the merge kernel
-    _check(_lib().ifx_attn_decode_bf16(_ptr(q), q_stride, _ptr(out), out.stride(0), _ptr(k_layer), _ptr(v_layer),
-                                       page_stride, page_size, _ptr(block_tables), block_tables.stride(0),
-                                       _ptr(dec_entries), n_dec, _ptr(entry_q_start), _ptr(entry_q_len),
-                                       _ptr(entry_ctx_start), _ptr(part_o), _ptr(part_ml), n_heads, n_kv, head_dim,
-                                       float(scale), int(window), int(n_splits), _stream()), "attn_decode_bf16")
+    _check(_lib().ifx_attn_decode_bf16_ex(_ptr(q), q_stride, _ptr(out), out.stride(0), _ptr(k_layer), _ptr(v_layer),
+                                          page_stride, page_size, _ptr(block_tables), block_tables.stride(0),
+                                          _ptr(dec_entries), n_dec, _ptr(entry_q_start), _ptr(entry_q_len),
+                                          _ptr(entry_ctx_start), _ptr(part_o), _ptr(part_ml), n_heads, n_kv, head_dim,
+                                          float(scale), int(window), int(n_splits), coef, every, _ptr(r1), _ptr(r2),
+                                          _stream()), "attn_decode_bf16")
     return out
 
 

@@ -52,7 +52,10 @@ PORTION_MIN = 8     # an entry with fewer new tokens than this is run token by t
 class QueryTiles:
     """How the attention kernels see the step, and the entry of every row: int32 device tensors.  ``single_*``: one
     (entry, place in the entry) per token of the entries with fewer than PORTION_MIN new tokens (decoded tokens
-    among them); ``tile_*`` and ``chunk_*``: the other entries cut into tiles of QUERY_TILE and of CHUNK_TILE tokens."""
+    among them); ``dec_entry``: the entries that bring exactly one token, and ``short_*``: the tokens of the other
+    entries below PORTION_MIN (the two together are ``single_*`` again, for mixers whose single tokens take the split
+    tensor-core kernel); ``tile_*`` and ``chunk_*``: the other entries cut into tiles of QUERY_TILE and of CHUNK_TILE
+    tokens."""
 
     single_entry: torch.Tensor
     single_q0: torch.Tensor
@@ -64,15 +67,25 @@ class QueryTiles:
     chunk_q0: torch.Tensor
     n_chunk: int
     row_entry: torch.Tensor
+    dec_entry: torch.Tensor = None
+    n_dec: int = 0
+    short_entry: torch.Tensor = None
+    short_q0: torch.Tensor = None
+    n_short: int = 0
 
 
 def describe_query_tiles(layout, put) -> QueryTiles:
     single_entry, single_q0, tile_entry, tile_q0, chunk_entry, chunk_q0 = [], [], [], [], [], []
+    dec_entry, short_entry, short_q0 = [], [], []
     for i in range(layout.n_entries):
         n = int(layout.q_len[i])
         if n < PORTION_MIN:
             for q0 in range(n):
                 single_entry.append(i), single_q0.append(q0)
+                if n > 1:
+                    short_entry.append(i), short_q0.append(q0)
+            if n == 1:
+                dec_entry.append(i)
             continue
         for q0 in range(0, n, QUERY_TILE):
             tile_entry.append(i), tile_q0.append(q0)
@@ -80,7 +93,8 @@ def describe_query_tiles(layout, put) -> QueryTiles:
             chunk_entry.append(i), chunk_q0.append(q0)
     rows = np.repeat(np.arange(layout.n_entries), layout.q_len[:layout.n_entries])
     return QueryTiles(put(single_entry), put(single_q0), len(single_entry), put(tile_entry), put(tile_q0), len(tile_entry),
-                      put(chunk_entry), put(chunk_q0), len(chunk_entry), put(rows))
+                      put(chunk_entry), put(chunk_q0), len(chunk_entry), put(rows), put(dec_entry), len(dec_entry),
+                      put(short_entry), put(short_q0), len(short_entry))
 
 
 class WindowAttention(Part):
@@ -253,11 +267,24 @@ class WindowAttention(Part):
         rest = (self.vdim, self.softcap, self.keep_first, self.sink, gate)
         more = dict(q_temp=self.q_temp, distance_toll=self.toll)
         pages = (k_layer, v_layer, page_stride, ctx.page_size, ctx.block_tables[g])
-        if step.n_single:       # decoded tokens and the shortest portions: a block a token and head
-            ops.attn_paged_options(q, q.stride(0), out, *pages, step.single_entry, step.single_q0, step.n_single, *common, *rest,
-                                   single_tokens=True, **more)
-        if step.n_chunk and (self.TENSOR_CORES and x.dtype == torch.bfloat16 and self.dim == self.vdim and out.is_contiguous()
-                             and self.dim in ops.FAST_ATTENTION_HEAD_DIMS):
+        fast = (self.TENSOR_CORES and x.dtype == torch.bfloat16 and self.dim == self.vdim and out.is_contiguous()
+                and self.dim in ops.FAST_ATTENTION_HEAD_DIMS)
+        singles = (step.single_entry, step.single_q0, step.n_single)
+        if fast and step.n_dec and not (self.softcap or self.keep_first or self.sink or self.gate):
+            # entries of one token: the split tensor-core kernel, which reads a key once for all the heads that share it
+            max_keys = min(ctx.max_ctx_len, self.window) if self.window else ctx.max_ctx_len
+            n_splits = ops.attn_decode_splits(step.n_dec, self.heads, self.kv_heads, self.dim, max_keys)
+            part_o = part_ml = None
+            if n_splits > 1:
+                part_o = torch.empty(step.n_dec * self.heads * n_splits * self.dim, dtype=torch.float32, device=x.device)
+                part_ml = torch.empty(step.n_dec * self.heads * n_splits * 2, dtype=torch.float32, device=x.device)
+            ops.attn_decode_bf16(q, q.stride(0), out, *pages, step.dec_entry, step.n_dec, ctx.entry_q_start, ctx.entry_q_len,
+                                 ctx.entry_ctx_start, part_o, part_ml, self.heads, self.kv_heads, self.dim, self.scale,
+                                 self.window, n_splits, **more)
+            singles = (step.short_entry, step.short_q0, step.n_short)
+        if singles[2]:          # decoded tokens and the shortest portions: a block a token and head
+            ops.attn_paged_options(q, q.stride(0), out, *pages, *singles, *common, *rest, single_tokens=True, **more)
+        if step.n_chunk and fast:
             ops.attn_prefill_options_bf16(q, q.stride(0), out, *pages, step.chunk_entry, step.chunk_q0, step.n_chunk, *common,
                                           self.softcap, self.keep_first, self.sink, gate, **more)      # portions on tensor cores
         elif step.n_tiles:
